@@ -4,8 +4,10 @@
 //  * attention_prepare: from the 32-bit rows [q | k | v] of a step (after projection, bias and any convolution): every q
 //    and k head optionally divided by its root mean square and multiplied by a gain of the head's size (shared by the
 //    heads), the first `rot` elements of every q and k head turned by angle = position * freq[i] (element i paired with
-//    i + rot/2; the angle is formed in 32-bit), queries written in the storage type, keys and values written into their
-//    pages. Keys are `dk` wide, values `dv`. One warp per (token, head of q, k or v).
+//    i + rot/2, or 2i with 2i + 1 in the interleaved layout; the angle is formed in 32-bit), then optionally every q and
+//    k head divided by its root mean square once more, without a gain (a norm AFTER the rotation), queries written in the
+//    storage type, keys and values written into their pages. Keys are `dk` wide, values `dv`; the values may be the keys
+//    as projected (before norm and rotation), the rows then hold [q | k] only. One warp per (token, head of q, k or v).
 //  * attention_flex: one warp per (token, query head). A query at position p of its request sees the keys j <= p,
 //    with a window only j > p - window, with a chunk only floor(j / chunk) == floor(p / chunk) (counted from the
 //    request's position 0). score = (q . k) * scale; with a cap c: c tanh(score / c); with slopes: minus
@@ -17,13 +19,16 @@
 constexpr int FX_MAX_D = 256;
 constexpr int FX_WARPS = 4;
 
+// flags of attention_prepare
+enum { FXP_INTERLEAVED = 1, FXP_UNIT_NORM_AFTER = 2, FXP_VALUES_ARE_KEYS = 4 };
+
 template <typename T>
 __global__ void __launch_bounds__(FX_WARPS * 32)
 attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ q_out, const float* __restrict__ q_gain,
                          const float* __restrict__ k_gain, float eps, const float* __restrict__ freq, int rot,
                          const int* __restrict__ positions, const int* __restrict__ req_index, const int* __restrict__ block_table,
                          int bt_stride, int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages,
-                         int tokens, int heads, int kv_heads, int dk, int dv, int writes) {
+                         int tokens, int heads, int kv_heads, int dk, int dv, int writes, int flags) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
     __shared__ float x_s[FX_WARPS][FX_MAX_D];
@@ -36,7 +41,9 @@ attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ 
     const bool is_q = s < heads, is_k = !is_q && s < heads + kv_heads;
     const int head = is_q ? s : (is_k ? s - heads : s - heads - kv_heads);
     const int d = (is_q || is_k) ? dk : dv;
-    const float* src = qkv + (size_t)t * ld + (is_q ? (size_t)head * dk : (is_k ? (size_t)heads * dk + (size_t)head * dk
+    // a value head that is the key head as projected reads the key's columns (the rows then hold no values)
+    const bool v_is_k = (flags & FXP_VALUES_ARE_KEYS) != 0;
+    const float* src = qkv + (size_t)t * ld + (is_q ? (size_t)head * dk : ((is_k || v_is_k) ? (size_t)heads * dk + (size_t)head * dk
                                                                                    : (size_t)(heads + kv_heads) * dk + (size_t)head * dv));
     T* dst = nullptr;
     if (is_q) {
@@ -61,37 +68,56 @@ attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ 
     for (int c = lane; c < d; c += 32) x_s[warp][c] = gain != nullptr ? src[c] * norm * gain[c] : src[c];
     __syncwarp();
     const int half = rot >> 1;
-    for (int c = lane; c < d; c += 32) {
-        float y = x_s[warp][c];
+    const bool interleaved = (flags & FXP_INTERLEAVED) != 0;
+    float y[FX_MAX_D / 32];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < FX_MAX_D / 32; ++j) {
+        const int c = lane + 32 * j;
+        if (c >= d) break;
+        float v = x_s[warp][c];
         if (c < rot) {
-            const int i = c < half ? c : c - half;
+            // the pair's first element is turned with minus, its second with plus; pairs are (i, i + rot/2) or (2i, 2i + 1)
+            const bool first = interleaved ? (c & 1) == 0 : c < half;
+            const int i = interleaved ? (c >> 1) : (c < half ? c : c - half);
+            const int mate = interleaved ? (c ^ 1) : (c < half ? c + half : c - half);
             const float a = (float)pos * freq[i];
             const float cs = cosf(a), sn = sinf(a);
-            y = c < half ? y * cs - x_s[warp][c + half] * sn : y * cs + x_s[warp][c - half] * sn;
+            v = first ? v * cs - x_s[warp][mate] * sn : v * cs + x_s[warp][mate] * sn;
         }
-        Elem<T>::store(dst + c, y);
+        y[j] = v;
+        ss = fmaf(v, v, ss);
+    }
+    float after = 1.0f;
+    if (flags & FXP_UNIT_NORM_AFTER) after = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
+#pragma unroll
+    for (int j = 0; j < FX_MAX_D / 32; ++j) {
+        const int c = lane + 32 * j;
+        if (c >= d) break;
+        Elem<T>::store(dst + c, y[j] * after);
     }
 }
 
 NIB_API int nib_attention_prepare(const float* qkv, int ld, void* q_out, const float* q_gain, const float* k_gain, float eps,
                                   const float* freq, int rot, const int* positions, const int* req_index, const int* block_table,
                                   int bt_stride, int page_size, void* k_pages, void* v_pages, int num_pages, int tokens, int heads,
-                                  int kv_heads, int dk, int dv, int writes, int dtype, cudaStream_t stream) {
+                                  int kv_heads, int dk, int dv, int writes, int dtype, int flags, cudaStream_t stream) {
     NIB_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0, "attention_prepare: bad head counts");
     NIB_REQUIRE(dk > 0 && dk <= FX_MAX_D && dv > 0 && dv <= FX_MAX_D, "attention_prepare: head sizes %d / %d are outside 1..%d", dk, dv, FX_MAX_D);
     NIB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dk && (rot == 0 || freq != nullptr), "attention_prepare: bad rotated width %d", rot);
     NIB_REQUIRE((q_gain == nullptr) == (k_gain == nullptr), "attention_prepare: q and k are normed together or not at all");
+    NIB_REQUIRE(!(flags & FXP_VALUES_ARE_KEYS) || dk == dv, "attention_prepare: values that are the keys have the keys' width");
     NIB_REQUIRE(!writes || (page_size > 0 && num_pages > 0 && block_table != nullptr), "attention_prepare: bad pages");
     if (tokens == 0) return 0;
     const dim3 grid(ceil_div((long long)tokens * (heads + 2 * kv_heads), FX_WARPS)), block(FX_WARPS * 32);
     if (dtype == NIB_F32)
         NIB_CUDA(launch_pdl(attention_prepare_kernel<float>, grid, block, (size_t)0, stream, qkv, ld, (float*)q_out, q_gain, k_gain, eps, freq, rot,
                             positions, req_index, block_table, bt_stride, page_size, (float*)k_pages, (float*)v_pages, num_pages, tokens, heads,
-                            kv_heads, dk, dv, writes));
+                            kv_heads, dk, dv, writes, flags));
     else if (dtype == NIB_BF16)
         NIB_CUDA(launch_pdl(attention_prepare_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, qkv, ld, (__nv_bfloat16*)q_out, q_gain, k_gain,
                             eps, freq, rot, positions, req_index, block_table, bt_stride, page_size, (__nv_bfloat16*)k_pages,
-                            (__nv_bfloat16*)v_pages, num_pages, tokens, heads, kv_heads, dk, dv, writes));
+                            (__nv_bfloat16*)v_pages, num_pages, tokens, heads, kv_heads, dk, dv, writes, flags));
     else
         NIB_REQUIRE(false, "attention_prepare: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();

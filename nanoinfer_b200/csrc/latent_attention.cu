@@ -6,8 +6,10 @@
 //   score_j = (q_lat . c_j + q_rot . kr_j) * scale,   out_h = W_uv,h (sum_j p_j c_j).
 // So a step reads each cached row once per (token, head) and the per-head matrices once per token.
 //
-// Rotation: interleaved pairs (2i, 2i+1), angle = position * freq[i] formed in 32-bit from a frequency vector that
-// the position encoding supplies (any scaling rule changes the vector only), cos and sin times a magnitude.
+// Rotation: interleaved pairs (2i, 2i+1) or, with `half_layout`, pairs (i, i + rot/2); angle = position * freq[i] formed
+// in 32-bit from a frequency vector that the position encoding supplies (any scaling rule changes the vector only),
+// cos and sin times a magnitude. With `sink` (one number per head) the softmax's denominator also holds exp(sink[head]):
+// a key without a value that every query sees once, not scaled.
 // Keys are taken in blocks of 32 that start at absolute multiples of 32 (online softmax), so a position's result
 // does not depend on how the request was cut into steps. All arithmetic is 32-bit; T is the storage type of the
 // cache and of the weights.
@@ -25,7 +27,7 @@ __global__ void __launch_bounds__(LAT_WARPS * 32)
 latent_store_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ gain, float eps,
                     const float* __restrict__ freq, float mag, const int* __restrict__ positions,
                     const int* __restrict__ req_index, const int* __restrict__ block_table, int bt_stride, int page_size,
-                    T* __restrict__ pages, int num_pages, int tokens, int rank, int rot) {
+                    T* __restrict__ pages, int num_pages, int tokens, int rank, int rot, int half_layout) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
     const int t = blockIdx.x * LAT_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -43,25 +45,26 @@ latent_store_kernel(const float* __restrict__ z, int ldz, const float* __restric
     for (int i = lane; i < rot / 2; i += 32) {
         const float ang = (float)pos * freq[i];
         const float cs = cosf(ang) * mag, sn = sinf(ang) * mag;
-        const float a = zr[rank + 2 * i], b = zr[rank + 2 * i + 1];
-        Elem<T>::store(row + rank + 2 * i, a * cs - b * sn);
-        Elem<T>::store(row + rank + 2 * i + 1, b * cs + a * sn);
+        const int ia = half_layout ? i : 2 * i, ib = half_layout ? i + rot / 2 : 2 * i + 1;
+        const float a = zr[rank + ia], b = zr[rank + ib];
+        Elem<T>::store(row + rank + ia, a * cs - b * sn);
+        Elem<T>::store(row + rank + ib, b * cs + a * sn);
     }
 }
 
 NIB_API int nib_latent_store(const float* z, int ldz, const float* gain, float eps, const float* freq, float mag,
                              const int* positions, const int* req_index, const int* block_table, int bt_stride,
                              int page_size, void* pages, int num_pages, int tokens, int rank, int rot, int dtype,
-                             cudaStream_t stream) {
+                             int half_layout, cudaStream_t stream) {
     NIB_REQUIRE(tokens >= 0 && rank > 0 && rot >= 0 && rot % 2 == 0 && page_size > 0, "latent_store: bad sizes");
     if (tokens == 0) return 0;
     const int grid = ceil_div(tokens, LAT_WARPS);
     if (dtype == NIB_F32)
         NIB_CUDA(launch_pdl(latent_store_kernel<float>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, z, ldz, gain, eps, freq, mag, positions, req_index,
-            block_table, bt_stride, page_size, (float*)pages, num_pages, tokens, rank, rot));
+            block_table, bt_stride, page_size, (float*)pages, num_pages, tokens, rank, rot, half_layout));
     else if (dtype == NIB_BF16)
         NIB_CUDA(launch_pdl(latent_store_kernel<__nv_bfloat16>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, z, ldz, gain, eps, freq, mag, positions, req_index,
-            block_table, bt_stride, page_size, (__nv_bfloat16*)pages, num_pages, tokens, rank, rot));
+            block_table, bt_stride, page_size, (__nv_bfloat16*)pages, num_pages, tokens, rank, rot, half_layout));
     else
         NIB_REQUIRE(false, "latent_store: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();
@@ -76,7 +79,8 @@ NIB_API int nib_latent_store(const float* z, int ldz, const float* gain, float e
 template <typename T, typename TQ>
 __global__ void __launch_bounds__(LAT_WARPS * 32)
 latent_query_kernel(const float* __restrict__ q, int ldq_in, const T* __restrict__ w_uk, const float* __restrict__ freq, float mag,
-                    const int* __restrict__ positions, TQ* __restrict__ qa, int ldq, int tokens, int heads, int dn, int rank, int rot) {
+                    const int* __restrict__ positions, TQ* __restrict__ qa, int ldq, int tokens, int heads, int dn, int rank, int rot,
+                    int half_layout) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
     const long long w = (long long)blockIdx.x * LAT_WARPS + (threadIdx.x >> 5);
@@ -106,9 +110,10 @@ latent_query_kernel(const float* __restrict__ q, int ldq_in, const T* __restrict
     for (int i = lane; i < rot / 2; i += 32) {
         const float ang = (float)pos * freq[i];
         const float cs = cosf(ang) * mag, sn = sinf(ang) * mag;
-        const float a = qr[dn + 2 * i], b = qr[dn + 2 * i + 1];
-        Elem<TQ>::store(o + rank + 2 * i, a * cs - b * sn);
-        Elem<TQ>::store(o + rank + 2 * i + 1, b * cs + a * sn);
+        const int ia = half_layout ? i : 2 * i, ib = half_layout ? i + rot / 2 : 2 * i + 1;
+        const float a = qr[dn + ia], b = qr[dn + ib];
+        Elem<TQ>::store(o + rank + ia, a * cs - b * sn);
+        Elem<TQ>::store(o + rank + ib, b * cs + a * sn);
     }
     for (int c = rank + rot + lane; c < ldq; c += 32) Elem<TQ>::store(o + c, 0.f);
 }
@@ -116,16 +121,16 @@ latent_query_kernel(const float* __restrict__ q, int ldq_in, const T* __restrict
 // dtype: the weights' type; q_dtype: the type of qa's elements; ldq: qa's row width per (token, head), >= rank + rot.
 NIB_API int nib_latent_query(const float* q, int ldq_in, const void* w_uk, const float* freq, float mag, const int* positions,
                              void* qa, int ldq, int q_dtype, int tokens, int heads, int dn, int rank, int rot, int dtype,
-                             cudaStream_t stream) {
+                             int half_layout, cudaStream_t stream) {
     NIB_REQUIRE(tokens >= 0 && heads > 0 && dn > 0 && rank > 0 && rot >= 0 && rot % 2 == 0 && ldq >= rank + rot, "latent_query: bad sizes");
     if (tokens == 0) return 0;
     const int grid = ceil_div((long long)tokens * heads, LAT_WARPS);
     if (dtype == NIB_F32 && q_dtype == NIB_F32)
-        NIB_CUDA(launch_pdl(latent_query_kernel<float, float>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, q, ldq_in, (const float*)w_uk, freq, mag, positions, (float*)qa, ldq, tokens, heads, dn, rank, rot));
+        NIB_CUDA(launch_pdl(latent_query_kernel<float, float>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, q, ldq_in, (const float*)w_uk, freq, mag, positions, (float*)qa, ldq, tokens, heads, dn, rank, rot, half_layout));
     else if (dtype == NIB_BF16 && q_dtype == NIB_F32)
-        NIB_CUDA(launch_pdl(latent_query_kernel<__nv_bfloat16, float>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, q, ldq_in, (const __nv_bfloat16*)w_uk, freq, mag, positions, (float*)qa, ldq, tokens, heads, dn, rank, rot));
+        NIB_CUDA(launch_pdl(latent_query_kernel<__nv_bfloat16, float>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, q, ldq_in, (const __nv_bfloat16*)w_uk, freq, mag, positions, (float*)qa, ldq, tokens, heads, dn, rank, rot, half_layout));
     else if (dtype == NIB_BF16 && q_dtype == NIB_BF16)
-        NIB_CUDA(launch_pdl(latent_query_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, q, ldq_in, (const __nv_bfloat16*)w_uk, freq, mag, positions, (__nv_bfloat16*)qa, ldq, tokens, heads, dn, rank, rot));
+        NIB_CUDA(launch_pdl(latent_query_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, q, ldq_in, (const __nv_bfloat16*)w_uk, freq, mag, positions, (__nv_bfloat16*)qa, ldq, tokens, heads, dn, rank, rot, half_layout));
     else
         NIB_REQUIRE(false, "latent_query: unsupported types %d / %d", dtype, q_dtype);
     NIB_LAUNCH_CHECK();
@@ -140,7 +145,8 @@ template <typename T>
 __global__ void __launch_bounds__(LAT_WARPS * 32)
 latent_attention_kernel(const float* __restrict__ qa, float* __restrict__ out, const int* __restrict__ positions,
                         const int* __restrict__ req_index, const int* __restrict__ block_table, int bt_stride, int page_size,
-                        const T* __restrict__ pages, int num_pages, int tokens, int heads, int rank, int rot, float scale, int window) {
+                        const T* __restrict__ pages, int num_pages, int tokens, int heads, int rank, int rot, float scale, int window,
+                        const float* __restrict__ sink) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
     __shared__ float q_s[LAT_WARPS][LAT_MAX_ROW];
@@ -194,6 +200,14 @@ latent_attention_kernel(const float* __restrict__ qa, float* __restrict__ out, c
         m_run = m_new;
     }
     float* o = out + (size_t)w * rank;
+    if (sink != nullptr) {      // one more term in the denominator; the sums are brought to the larger of the two maxima
+        const float sk = sink[(int)(w % heads)];
+        const float m_fin = fmaxf(m_run, sk);
+        const float f = (m_run == -INFINITY) ? 0.f : expf(m_run - m_fin);
+        l_run = l_run * f + expf(sk - m_fin);
+#pragma unroll
+        for (int i = 0; i < LAT_MAX_RANK / 32; ++i) acc[i] *= f;
+    }
     const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
 #pragma unroll
     for (int i = 0; i < LAT_MAX_RANK / 32; ++i) {
@@ -205,7 +219,7 @@ latent_attention_kernel(const float* __restrict__ qa, float* __restrict__ out, c
 NIB_API int nib_latent_attention(const float* qa, float* out, const int* positions, const int* req_index,
                                  const int* block_table, int bt_stride, int page_size, const void* pages, int num_pages,
                                  int tokens, int heads, int rank, int rot, float scale, int window, int dtype,
-                                 cudaStream_t stream) {
+                                 const float* sink, cudaStream_t stream) {
     NIB_REQUIRE(tokens >= 0 && heads > 0 && rank > 0 && rank <= LAT_MAX_RANK && rank + rot <= LAT_MAX_ROW,
                 "latent attention: latent %d (+%d rotated) is outside 1..%d (row up to %d)", rank, rot, LAT_MAX_RANK, LAT_MAX_ROW);
     NIB_REQUIRE(page_size > 0 && num_pages > 0 && window >= 0, "latent attention: bad page_size/num_pages/window");
@@ -213,10 +227,10 @@ NIB_API int nib_latent_attention(const float* qa, float* out, const int* positio
     const int grid = ceil_div((long long)tokens * heads, LAT_WARPS);
     if (dtype == NIB_F32)
         NIB_CUDA(launch_pdl(latent_attention_kernel<float>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, qa, out, positions, req_index, block_table, bt_stride,
-            page_size, (const float*)pages, num_pages, tokens, heads, rank, rot, scale, window));
+            page_size, (const float*)pages, num_pages, tokens, heads, rank, rot, scale, window, sink));
     else if (dtype == NIB_BF16)
         NIB_CUDA(launch_pdl(latent_attention_kernel<__nv_bfloat16>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, qa, out, positions, req_index, block_table, bt_stride,
-            page_size, (const __nv_bfloat16*)pages, num_pages, tokens, heads, rank, rot, scale, window));
+            page_size, (const __nv_bfloat16*)pages, num_pages, tokens, heads, rank, rot, scale, window, sink));
     else
         NIB_REQUIRE(false, "latent attention: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();
@@ -225,11 +239,12 @@ NIB_API int nib_latent_attention(const float* qa, float* out, const int* positio
 
 // ---------------------------------------------------------------------------------- values out of the latent space
 // lat: [tokens, heads, rank] floats; w_uv: [heads*dv, rank] as stored; out: [tokens, heads*dv] of T:
-//   out[t, h*dv + j] = sum_c w_uv[h*dv + j, c] * lat[t, h, c].   One warp per (token, head).
+//   out[t, h*dv + j] = sum_c w_uv[h*dv + j, c] * lat[t, h, c], times sigmoid(gate[t, h*dv + j]) with a gate.
+// One warp per (token, head).
 template <typename T>
 __global__ void __launch_bounds__(LAT_WARPS * 32)
 latent_value_kernel(const float* __restrict__ lat, const T* __restrict__ w_uv, T* __restrict__ out, int ldo, int tokens,
-                    int heads, int dv, int rank) {
+                    int heads, int dv, int rank, const float* __restrict__ gate, int ldg) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
     __shared__ float l_s[LAT_WARPS][LAT_MAX_RANK];
@@ -244,19 +259,22 @@ latent_value_kernel(const float* __restrict__ lat, const T* __restrict__ w_uv, T
         float acc = 0.f;
         for (int c = lane; c < rank; c += 32) acc = fmaf(Elem<T>::load(wr + c), l_s[warp][c], acc);
         acc = warp_sum(acc);
-        if (lane == 0) Elem<T>::store(out + (size_t)t * ldo + (size_t)h * dv + j, acc);
+        if (lane == 0) {
+            if (gate != nullptr) acc *= 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + (size_t)h * dv + j]));
+            Elem<T>::store(out + (size_t)t * ldo + (size_t)h * dv + j, acc);
+        }
     }
 }
 
 NIB_API int nib_latent_value(const float* lat, const void* w_uv, void* out, int ldo, int tokens, int heads, int dv, int rank,
-                             int dtype, cudaStream_t stream) {
+                             int dtype, const float* gate, int ldg, cudaStream_t stream) {
     NIB_REQUIRE(tokens >= 0 && heads > 0 && dv > 0 && rank > 0 && rank <= LAT_MAX_RANK, "latent_value: bad sizes");
     if (tokens == 0) return 0;
     const int grid = ceil_div((long long)tokens * heads, LAT_WARPS);
     if (dtype == NIB_F32)
-        NIB_CUDA(launch_pdl(latent_value_kernel<float>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, lat, (const float*)w_uv, (float*)out, ldo, tokens, heads, dv, rank));
+        NIB_CUDA(launch_pdl(latent_value_kernel<float>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, lat, (const float*)w_uv, (float*)out, ldo, tokens, heads, dv, rank, gate, ldg));
     else if (dtype == NIB_BF16)
-        NIB_CUDA(launch_pdl(latent_value_kernel<__nv_bfloat16>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, lat, (const __nv_bfloat16*)w_uv, (__nv_bfloat16*)out, ldo, tokens, heads, dv, rank));
+        NIB_CUDA(launch_pdl(latent_value_kernel<__nv_bfloat16>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, lat, (const __nv_bfloat16*)w_uv, (__nv_bfloat16*)out, ldo, tokens, heads, dv, rank, gate, ldg));
     else
         NIB_REQUIRE(false, "latent_value: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();

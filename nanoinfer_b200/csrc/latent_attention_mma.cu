@@ -93,7 +93,8 @@ template <int DKP, int DVP>
 __global__ void __launch_bounds__(LM_WARPS * 32, DKP <= 160 ? 3 : 2)
 latent_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qa, float* __restrict__ out, const int* __restrict__ q_start,
                           const int* __restrict__ ctx_lens, const int* __restrict__ block_table, int bt_stride, int page_size,
-                          const __nv_bfloat16* __restrict__ pages, int num_pages, int heads, int rank, int width, float scale, int window) {
+                          const __nv_bfloat16* __restrict__ pages, int num_pages, int heads, int rank, int width, float scale, int window,
+                          const float* __restrict__ sink) {
         pdl_wait();      // everything this kernel reads may come from the kernel before
     extern __shared__ __align__(16) unsigned char smem[];
     const int req = blockIdx.y;
@@ -110,11 +111,13 @@ latent_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qa, float* __restric
     int vis_lo[2], vis_hi[2];
     const __nv_bfloat16* q_ptr[2];
     long long out_off[2];
+    float sink2[2] = {0.f, 0.f};        // the head's sink in the units of the running maximum (log2)
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = row0 + warp * 16 + g + 8 * r;
         if (row < rows_total) {
             const int ti = row / heads, head = row - ti * heads;
+            if (sink != nullptr) sink2[r] = sink[head] * LOG2E;
             const int p = pos0 + ti;
             vis_hi[r] = p;
             vis_lo[r] = window > 0 ? max(0, p - window + 1) : 0;
@@ -162,7 +165,13 @@ latent_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qa, float* __restric
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         if (out_off[r] < 0) continue;
-        const float inv = l_run[r] > 0.f ? 1.0f / l_run[r] : 0.f;
+        float l = l_run[r], f = 1.0f;
+        if (sink != nullptr) {      // one more term in the denominator, at the larger of the two maxima
+            const float m_fin = fmaxf(m_run[r], sink2[r]);
+            f = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - m_fin);
+            l = l * f + exp2f(sink2[r] - m_fin);
+        }
+        const float inv = l > 0.f ? f / l : 0.f;
         float* orow = out + out_off[r];
 #pragma unroll
         for (int d = 0; d < DVP / 8; ++d)
@@ -179,7 +188,7 @@ __global__ void __launch_bounds__(LM_WARPS * 32)
 latent_decode_mma_kernel(const __nv_bfloat16* __restrict__ qa, float* __restrict__ out, const int* __restrict__ ctx_lens,
                          const int* __restrict__ block_table, int bt_stride, int page_size, const __nv_bfloat16* __restrict__ pages,
                          int num_pages, int heads, int rank, int width, float scale, int window, int splits,
-                         float* __restrict__ part_o, float* __restrict__ part_ml) {
+                         float* __restrict__ part_o, float* __restrict__ part_ml, const float* __restrict__ sink) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
     extern __shared__ __align__(16) unsigned char smem[];
@@ -262,6 +271,12 @@ latent_decode_mma_kernel(const __nv_bfloat16* __restrict__ qa, float* __restrict
         }
         const int head = h0 + row;
         if (splits == 1) {
+            if (sink != nullptr) {
+                const float s2 = sink[head] * LOG2E, m_fin = fmaxf(m, s2);
+                const float f = (m == -INFINITY) ? 0.f : exp2f(m - m_fin);
+                l = l * f + exp2f(s2 - m_fin);
+                acc *= f;
+            }
             if (d < rank) out[((size_t)token * heads + head) * rank + d] = l > 0.f ? acc / l : 0.f;
         } else {
             const size_t slot = ((size_t)token * heads + head) * splits + split;
@@ -274,14 +289,16 @@ latent_decode_mma_kernel(const __nv_bfloat16* __restrict__ qa, float* __restrict
 // Merges the splits of every (token, head) in split order. One warp per (token, head).
 __global__ void __launch_bounds__(128)
 latent_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, float* __restrict__ out,
-                             int rows, int splits, int dvp, int rank) {
+                             int rows, int splits, int dvp, int rank, const float* __restrict__ sink, int heads) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
     const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (w >= rows) return;
     float m = -INFINITY;
     for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[((size_t)w * splits + s) * 2]);
-    float l = 0.f;
+    const float sink2 = sink != nullptr ? sink[w % heads] * LOG2E : -INFINITY;
+    m = fmaxf(m, sink2);        // the sink is one more part: a sum of exp(sink) at its own maximum, no output
+    float l = sink != nullptr ? exp2f(sink2 - m) : 0.f;
     for (int s = 0; s < splits; ++s) {
         const float ms = part_ml[((size_t)w * splits + s) * 2];
         if (ms != -INFINITY) l += part_ml[((size_t)w * splits + s) * 2 + 1] * exp2f(ms - m);
@@ -300,13 +317,13 @@ latent_decode_combine_kernel(const float* __restrict__ part_o, const float* __re
 template <int DKP, int DVP>
 int lm_launch(bool decode, const __nv_bfloat16* qa, float* out, const int* q_start, const int* ctx_lens, const int* bt, int bt_stride,
               int page_size, const __nv_bfloat16* pages, int num_pages, int requests, int max_q_len, int heads, int rank, int width,
-              float scale, int window, int splits, float* part_o, float* part_ml, cudaStream_t stream) {
+              float scale, int window, int splits, float* part_o, float* part_ml, const float* sink, cudaStream_t stream) {
     if (!decode) {
         const size_t smem = 2 * (size_t)LTile<DKP>::BYTES;
         NIB_CUDA(cudaFuncSetAttribute(latent_prefill_mma_kernel<DKP, DVP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         const dim3 grid(ceil_div((long long)max_q_len * heads, LM_WARPS * 16), requests);
         NIB_CUDA(launch_pdl(latent_prefill_mma_kernel<DKP, DVP>, dim3(grid), dim3(LM_WARPS * 32), (size_t)(smem), stream, qa, out, q_start, ctx_lens, bt, bt_stride, page_size,
-                                                                                   pages, num_pages, heads, rank, width, scale, window));
+                                                                                   pages, num_pages, heads, rank, width, scale, window, sink));
         NIB_LAUNCH_CHECK();
         return 0;
     }
@@ -316,11 +333,11 @@ int lm_launch(bool decode, const __nv_bfloat16* qa, float* out, const int* q_sta
     NIB_CUDA(cudaFuncSetAttribute(latent_decode_mma_kernel<DKP, DVP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const dim3 grid(splits, requests, ceil_div(heads, 16));
     NIB_CUDA(launch_pdl(latent_decode_mma_kernel<DKP, DVP>, dim3(grid), dim3(LM_WARPS * 32), (size_t)(smem), stream, qa, out, ctx_lens, bt, bt_stride, page_size, pages, num_pages,
-                                                                              heads, rank, width, scale, window, splits, part_o, part_ml));
+                                                                              heads, rank, width, scale, window, splits, part_o, part_ml, sink));
     NIB_LAUNCH_CHECK();
     if (splits > 1) {
         const int rows = requests * heads;
-        NIB_CUDA(launch_pdl(latent_decode_combine_kernel, dim3(ceil_div(rows, 4)), dim3(128), (size_t)(0), stream, part_o, part_ml, out, rows, splits, DVP, rank));
+        NIB_CUDA(launch_pdl(latent_decode_combine_kernel, dim3(ceil_div(rows, 4)), dim3(128), (size_t)(0), stream, part_o, part_ml, out, rows, splits, DVP, rank, sink, heads));
         NIB_LAUNCH_CHECK();
     }
     return 0;
@@ -361,7 +378,8 @@ __device__ __forceinline__ void lm_a_from_f32(unsigned (&a)[4], const float* con
 template <int KP, typename TO>
 __global__ void __launch_bounds__(LM_WARPS * 32)
 head_product_nk_kernel(const float* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, const float* __restrict__ bias,
-                       TO* __restrict__ out, int ldo, long long out_head_stride, int tokens, int n, int k) {
+                       TO* __restrict__ out, int ldo, long long out_head_stride, int tokens, int n, int k,
+                       const float* __restrict__ gate, int ldg) {
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -401,7 +419,13 @@ head_product_nk_kernel(const float* __restrict__ a, int lda, const __nv_bfloat16
                 const int f = n0 + j * 8 + 2 * t4;
                 if (f >= n) continue;
                 if constexpr (sizeof(TO) == 2) {
-                    *reinterpret_cast<unsigned*>(o + j * 8 + 2 * t4) = pack_bf16(s[j][2 * r], s[j][2 * r + 1]);
+                    float v0 = s[j][2 * r], v1 = s[j][2 * r + 1];
+                    if (gate != nullptr) {      // times sigmoid(gate) at the output's own place (heads side by side, n wide)
+                        const float* gr = gate + (size_t)tok[r] * ldg + (size_t)h * n + f;
+                        v0 *= 1.0f / (1.0f + expf(-gr[0]));
+                        v1 *= 1.0f / (1.0f + expf(-gr[1]));
+                    }
+                    *reinterpret_cast<unsigned*>(o + j * 8 + 2 * t4) = pack_bf16(v0, v1);
                 } else {
                     const float b0 = bias ? bias[(size_t)h * n + f] : 0.f, b1 = bias ? bias[(size_t)h * n + f + 1] : 0.f;
                     *reinterpret_cast<float2*>(o + j * 8 + 2 * t4) = make_float2(s[j][2 * r] + b0, s[j][2 * r + 1] + b1);
@@ -412,13 +436,13 @@ head_product_nk_kernel(const float* __restrict__ a, int lda, const __nv_bfloat16
 }
 
 // qa[t, h, c] = sum_d q[t, h, d] * w[h, d, c] for c < n (w: [heads, k, n] bfloat16, its rows are the inputs), then the
-// rotated part: qa[t, h, n + 2i], [.. + 1] = the pair q[t, h, k + 2i], [.. + 1] turned by position * freq[i], and zeros up
-// to ldq. grid: (token tiles of 64, heads). q: floats, `ldq_in` elements per token, a head's k + rot values together.
+// rotated part: qa[t, h, n + 2i], [.. + 1] = the pair q[t, h, k + 2i], [.. + 1] turned by position * freq[i] (with
+// half_layout the pair is i, i + rot/2), and zeros up to ldq. grid: (token tiles of 64, heads). q: floats, `ldq_in` elements per token, a head's k + rot values together.
 template <int KP>
 __global__ void __launch_bounds__(LM_WARPS * 32)
 head_product_kn_kernel(const float* __restrict__ q, int ldq_in, const __nv_bfloat16* __restrict__ w, const float* __restrict__ freq,
                        float mag, const int* __restrict__ positions, __nv_bfloat16* __restrict__ qa, int ldq, int tokens, int heads,
-                       int n, int k, int rot) {
+                       int n, int k, int rot, int half_layout) {
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -469,9 +493,10 @@ head_product_kn_kernel(const float* __restrict__ q, int ldq_in, const __nv_bfloa
         for (int i = lane; i < rot / 2; i += 32) {
             const float ang = pos * freq[i];
             const float cs = cosf(ang) * mag, sn = sinf(ang) * mag;
-            const float x = qr[2 * i], y = qr[2 * i + 1];
-            dst[2 * i] = __float2bfloat16_rn(x * cs - y * sn);
-            dst[2 * i + 1] = __float2bfloat16_rn(y * cs + x * sn);
+            const int ia = half_layout ? i : 2 * i, ib = half_layout ? i + rot / 2 : 2 * i + 1;
+            const float x = qr[ia], y = qr[ib];
+            dst[ia] = __float2bfloat16_rn(x * cs - y * sn);
+            dst[ib] = __float2bfloat16_rn(y * cs + x * sn);
         }
         for (int c = n + rot + lane; c < ldq; c += 32) qa[((size_t)token * heads + h) * ldq + c] = __float2bfloat16_rn(0.f);
     }
@@ -488,12 +513,13 @@ NIB_API int nib_latent_attention_mma_supported(int rank, int rot) {
 // The padded query row width the kernels read (zeros beyond rank + rot).
 NIB_API int nib_latent_attention_mma_qwidth(int rank, int rot) { return (rank + rot + 15) / 16 * 16; }
 
-// decode != 0: every request brings one token (q_start is not read); part_o / part_ml: scratch for splits > 1
+// decode != 0: every request brings one token (q_start is not read); part_o / part_ml: scratch for splits > 1;
+// sink: nullptr, or one number per head whose exponential joins every row's softmax denominator
 // ([requests, heads, splits, dvp] and [requests, heads, splits, 2] floats, dvp <= 192).
 NIB_API int nib_latent_attention_mma(int decode, const void* qa, void* out, const int* q_start, const int* ctx_lens,
                                      const int* block_table, int bt_stride, int page_size, const void* pages, int num_pages,
                                      int requests, int max_q_len, int heads, int rank, int rot, float scale, int window,
-                                     int splits, float* part_o, float* part_ml, cudaStream_t stream) {
+                                     int splits, float* part_o, float* part_ml, const float* sink, cudaStream_t stream) {
     NIB_REQUIRE(nib_latent_attention_mma_supported(rank, rot) == 1, "latent attention (tensor cores): latent %d + %d is not supported", rank, rot);
     NIB_REQUIRE(requests >= 0 && heads > 0 && page_size > 0 && num_pages > 0 && window >= 0 && splits >= 1, "latent attention (tensor cores): bad sizes");
     NIB_REQUIRE(!decode || splits == 1 || (part_o != nullptr && part_ml != nullptr), "latent attention (tensor cores): splits need scratch");
@@ -503,7 +529,7 @@ NIB_API int nib_latent_attention_mma(int decode, const void* qa, void* out, cons
     if (dkp == DKP && dvp == DVP)                                                                                                 \
         return lm_launch<DKP, DVP>(decode != 0, (const __nv_bfloat16*)qa, (float*)out, q_start, ctx_lens, block_table,   \
                                    bt_stride, page_size, (const __nv_bfloat16*)pages, num_pages, requests, max_q_len, heads, rank, \
-                                   width, scale, window, splits, part_o, part_ml, stream);
+                                   width, scale, window, splits, part_o, part_ml, sink, stream);
     NIB_LM(16, 16) NIB_LM(32, 32) NIB_LM(48, 32) NIB_LM(48, 48) NIB_LM(64, 32) NIB_LM(64, 64) NIB_LM(80, 32) NIB_LM(80, 64) NIB_LM(80, 80)
     NIB_LM(96, 32) NIB_LM(96, 64) NIB_LM(96, 96) NIB_LM(112, 32) NIB_LM(112, 64) NIB_LM(112, 112) NIB_LM(128, 32) NIB_LM(128, 64) NIB_LM(128, 128)
     NIB_LM(144, 64) NIB_LM(144, 128) NIB_LM(160, 64) NIB_LM(160, 128) NIB_LM(176, 64) NIB_LM(176, 128) NIB_LM(192, 64) NIB_LM(192, 128)
@@ -523,8 +549,10 @@ NIB_API int nib_head_product_supported(int kn_layout, int k, int n) {
 // n = value width, bfloat16 out), or the gates of a block-diagonal map (float out with bias, out_f32 != 0). The head's
 // outputs of token t start at out + t * ldo + h * out_head_stride (elements).
 NIB_API int nib_head_product_nk(const float* a, int lda, const void* w, const float* bias, void* out, int ldo,
-                                long long out_head_stride, int out_f32, int tokens, int heads, int n, int k, cudaStream_t stream) {
+                                long long out_head_stride, int out_f32, int tokens, int heads, int n, int k, const float* gate, int ldg,
+                                cudaStream_t stream) {
     NIB_REQUIRE(nib_head_product_supported(0, k, n) == 1 && tokens >= 0 && heads > 0, "per-head product: sizes k=%d n=%d are not supported", k, n);
+    NIB_REQUIRE(gate == nullptr || !out_f32, "per-head product: the gate goes with outputs in the storage type");
     if (tokens == 0) return 0;
     const dim3 grid(ceil_div(tokens, LM_WARPS * 16), heads);
     const int kp = (k + 15) / 16 * 16;
@@ -532,10 +560,10 @@ NIB_API int nib_head_product_nk(const float* a, int lda, const void* w, const fl
     if (kp == KP) {                                                                                                                 \
         if (out_f32)                                                                                                                \
             NIB_CUDA(launch_pdl(head_product_nk_kernel<KP, float>, grid, dim3(LM_WARPS * 32), (size_t)LTile<KP>::BYTES, stream, a, lda, \
-                                (const __nv_bfloat16*)w, bias, (float*)out, ldo, out_head_stride, tokens, n, k));                  \
+                                (const __nv_bfloat16*)w, bias, (float*)out, ldo, out_head_stride, tokens, n, k, gate, ldg));       \
         else                                                                                                                        \
             NIB_CUDA(launch_pdl(head_product_nk_kernel<KP, __nv_bfloat16>, grid, dim3(LM_WARPS * 32), (size_t)LTile<KP>::BYTES, stream, a, lda, \
-                                (const __nv_bfloat16*)w, bias, (__nv_bfloat16*)out, ldo, out_head_stride, tokens, n, k));          \
+                                (const __nv_bfloat16*)w, bias, (__nv_bfloat16*)out, ldo, out_head_stride, tokens, n, k, gate, ldg)); \
         return 0;                                                                                                                   \
     }
     NIB_HP(16) NIB_HP(32) NIB_HP(48) NIB_HP(64) NIB_HP(80) NIB_HP(96) NIB_HP(112) NIB_HP(128) NIB_HP(144) NIB_HP(160) NIB_HP(176) NIB_HP(192)
@@ -547,7 +575,7 @@ NIB_API int nib_head_product_nk(const float* a, int lda, const void* w, const fl
 // qa[t, h] = [q[t, h, :k] . w[h] | q[t, h, k:] rotated | zeros], w: [heads, k, n] (queries into the latent space:
 // k = the head's plain width, n = latent); qa: bfloat16 rows of ldq elements per (token, head).
 NIB_API int nib_head_product_kn(const float* q, int ldq_in, const void* w, const float* freq, float mag, const int* positions,
-                                void* qa, int ldq, int tokens, int heads, int n, int k, int rot, cudaStream_t stream) {
+                                void* qa, int ldq, int tokens, int heads, int n, int k, int rot, int half_layout, cudaStream_t stream) {
     NIB_REQUIRE(nib_head_product_supported(1, k, n) == 1 && tokens >= 0 && heads > 0 && rot % 2 == 0 && ldq >= n + rot,
                 "per-head product: sizes k=%d n=%d are not supported", k, n);
     if (tokens == 0) return 0;
@@ -556,7 +584,7 @@ NIB_API int nib_head_product_kn(const float* q, int ldq_in, const void* w, const
 #define NIB_HP(KP)                                                                                                                   \
     if (kp == KP) {                                                                                                                  \
         NIB_CUDA(launch_pdl(head_product_kn_kernel<KP>, grid, dim3(LM_WARPS * 32), (size_t)(KP * LTile<LM_BLOCK_N>::ROW_BYTES), stream, \
-                            q, ldq_in, (const __nv_bfloat16*)w, freq, mag, positions, (__nv_bfloat16*)qa, ldq, tokens, heads, n, k, rot)); \
+                            q, ldq_in, (const __nv_bfloat16*)w, freq, mag, positions, (__nv_bfloat16*)qa, ldq, tokens, heads, n, k, rot, half_layout)); \
         return 0;                                                                                                                    \
     }
     NIB_HP(16) NIB_HP(32) NIB_HP(48) NIB_HP(64) NIB_HP(80) NIB_HP(96) NIB_HP(112) NIB_HP(128)

@@ -21,6 +21,7 @@ class KernelError(RuntimeError):
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 _EPI = {"store": 0, "add": 1, "f32": 2, "swiglu": 3}
+_LAYOUT = {"interleaved": 0, "half": 1}     # which elements of a rotated vector make a pair
 
 
 def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
@@ -86,7 +87,8 @@ class Kernels:
                      "nib_latent_attention_mma_qwidth", "nib_block_diag_smallm", "nib_rmsnorm_pair", "nib_rmsnorm_pair_supported", "nib_head_product_supported",
                      "nib_head_product_nk", "nib_head_product_kn", "nib_depth_mix_norm_pair", "nib_embed_scaled", "nib_gated_norm",
                      "nib_linear_state_scan", "nib_conv_tokens", "nib_conv_tail", "nib_conv_step", "nib_token_shift", "nib_decay_map", "nib_step_sizes",
-                     "nib_attention_prepare", "nib_attention_flex", "nib_attention_flex_mma", "nib_attention_flex_mma_supported"):
+                     "nib_attention_prepare", "nib_attention_flex", "nib_attention_flex_mma", "nib_attention_flex_mma_supported",
+                     "nib_rmsnorm_add", "nib_moe_route", "nib_moe_max_tiles", "nib_moe_group", "nib_moe_gemm_simt", "nib_moe_combine"):
             getattr(self._lib, name).restype = c_int
 
     # ---- plumbing ---------------------------------------------------------------------------
@@ -659,11 +661,71 @@ class Kernels:
             if tuple(a32.shape) != (m, nb * k):
                 raise KernelError("block_diag_linear: a32 does not fit")
             self._check(self._lib.nib_head_product_nk(_ptr(a32), c_int(nb * k), _ptr(w_blocks), _ptr(bias32), _ptr(out32), c_int(n),
-                                                      c_longlong(m * n), c_int(1), c_int(m), c_int(nb), c_int(n), c_int(k), self._stream()),
-                        "block-diagonal product (tensor cores)")
+                                                      c_longlong(m * n), c_int(1), c_int(m), c_int(nb), c_int(n), c_int(k), _ptr(None), c_int(0),
+                                                      self._stream()), "block-diagonal product (tensor cores)")
             return
         for b in range(nb):
             self.linear(a_blocks[b], w_blocks[b], None if bias32 is None else bias32[b], out32[b], "f32")
+
+    def rmsnorm_add(self, y32, gain32, eps, mult, x32, h_out=None, clear=False):
+        """x32 += mult * y32 / rms(y32) * gain32, row by row (``eps`` inside the root): the residual sum of a block whose norm
+        stands on a sublayer's output. ``h_out``: the new x32 also in that tensor's type. ``clear``: y32 is left zeroed."""
+        self._rows(y32, torch.float32, "rmsnorm_add y"); self._rows(x32, torch.float32, "rmsnorm_add x"); _need(gain32, torch.float32, "rmsnorm_add gain")
+        m, n = x32.shape
+        if tuple(y32.shape) != (m, n) or gain32.numel() != n or not y32.is_contiguous() or not x32.is_contiguous():
+            raise KernelError("rmsnorm_add: shapes do not fit")
+        if h_out is not None:
+            _need(h_out, None, "rmsnorm_add h")
+            if tuple(h_out.shape) != (m, n):
+                raise KernelError("rmsnorm_add: h_out has the stream's shape")
+        self._check(self._lib.nib_rmsnorm_add(_ptr(y32), _ptr(gain32), _ptr(x32), _ptr(h_out), c_int(m), c_int(n), c_float(eps), c_float(mult),
+                                              c_int(1 if clear else 0), c_int(_DT[h_out.dtype] if h_out is not None else 0), self._stream()),
+                    "rmsnorm_add")
+
+    # ---- routed experts (moe.cu) ---------------------------------------------------------------------------
+    def moe_route(self, z32, top, sel_e, sel_w):
+        """From the router logits z32 [tokens, experts]: sel_e [tokens, top] int32 = the experts with the largest logits (the
+        first of equal ones), sel_w [tokens, top] = sigmoid of their logits."""
+        self._rows(z32, torch.float32, "moe_route z"); _need(sel_e, torch.int32, "moe_route experts"); _need(sel_w, torch.float32, "moe_route weights")
+        m, experts = z32.shape
+        if tuple(sel_e.shape) != (m, top) or tuple(sel_w.shape) != (m, top):
+            raise KernelError("moe_route: shapes do not fit")
+        self._check(self._lib.nib_moe_route(_ptr(z32), c_int(z32.stride(0)), _ptr(sel_e), _ptr(sel_w), c_int(m), c_int(experts), c_int(top),
+                                            self._stream()), "moe_route")
+
+    def moe_experts(self, h, sel_e, sel_w, w_gate_up, w_down, out32):
+        """out32[t] += sum over the token's choices c of W_down,e (silu(W_gate,e x) * (W_up,e x)) with e = sel_e[t, c] and
+        x = sel_w[t, c] * h[t]: the weight stands on the expert's input. w_gate_up [experts, 2 ff, hidden] (gate rows, then up
+        rows), w_down [experts, hidden, ff]. The choices are summed in ascending order."""
+        _need(h, None, "moe_experts h"); _need(w_gate_up, h.dtype, "moe_experts w_gate_up"); _need(w_down, h.dtype, "moe_experts w_down")
+        _need(sel_e, torch.int32, "moe_experts experts"); _need(sel_w, torch.float32, "moe_experts weights"); _need(out32, torch.float32, "moe_experts out")
+        m, hidden = h.shape
+        experts, ff2, _ = w_gate_up.shape
+        ff, top = ff2 // 2, sel_e.shape[1]
+        if tuple(w_gate_up.shape) != (experts, 2 * ff, hidden) or tuple(w_down.shape) != (experts, hidden, ff) or tuple(out32.shape) != (m, hidden) \
+                or tuple(sel_e.shape) != (m, top) or tuple(sel_w.shape) != (m, top):
+            raise KernelError("moe_experts: shapes do not fit")
+        if m == 0:
+            return
+        n, dev, dt = m * top, h.device, c_int(_DT[h.dtype])
+        tile_rows = 64
+        max_tiles = self._lib.nib_moe_max_tiles(c_int(n), c_int(experts), c_int(tile_rows))
+        idx = torch.empty(2 * n + 3 * max_tiles + 1, dtype=torch.int32, device=dev)
+        row_of, src_of, tiles, n_tiles = idx[:n], idx[n:2 * n], idx[2 * n:2 * n + 3 * max_tiles], idx[2 * n + 3 * max_tiles:]
+        self._check(self._lib.nib_moe_group(_ptr(sel_e), c_int(n), c_int(experts), c_int(tile_rows), _ptr(row_of), _ptr(src_of), _ptr(tiles),
+                                            _ptr(n_tiles), c_int(max_tiles), self._stream()), "moe_group")
+        act = torch.empty((n, ff), dtype=h.dtype, device=dev)
+        self._check(self._lib.nib_moe_gemm_simt(c_int(1), _ptr(h), c_int(h.stride(0)), _ptr(w_gate_up), _ptr(act), c_int(ff), _ptr(tiles), _ptr(n_tiles),
+                                                c_int(max_tiles), _ptr(src_of), _ptr(sel_w), c_int(top), c_int(ff), c_int(hidden), c_int(0), dt,
+                                                self._stream()), "experts: gate, up, activation")
+        scatter = top == 1      # one choice per token: its result goes straight into the token's row
+        y = out32 if scatter else torch.empty((n, hidden), dtype=torch.float32, device=dev)
+        self._check(self._lib.nib_moe_gemm_simt(c_int(0), _ptr(act), c_int(ff), _ptr(w_down), _ptr(y), c_int(y.stride(0)), _ptr(tiles), _ptr(n_tiles),
+                                                c_int(max_tiles), _ptr(src_of), _ptr(sel_w), c_int(top), c_int(hidden), c_int(ff), c_int(1 if scatter else 0),
+                                                dt, self._stream()), "experts: down")
+        if not scatter:
+            self._check(self._lib.nib_moe_combine(_ptr(y), _ptr(row_of), _ptr(out32), c_int(m), c_int(hidden), c_int(top), self._stream()),
+                        "experts: sum of a token's choices")
 
     # ---- gate, norm in groups, skip (pointwise.cu) ---------------------------------------------------------
     def gated_norm(self, o32, out, groups=0, eps=0.0, gain32=None, gate32=None, gate_kind="none", gate_first=False,
@@ -838,14 +900,19 @@ class Kernels:
 
     # ---- attention with options (attention_flex.cu) --------------------------------------------------------
     def attention_prepare(self, qkv32, q_out, heads, kv_heads, dim, vdim, q_gain32, k_gain32, eps, freq32, rot_dims, ctx,
-                          block_table, page_size, k_pages, v_pages, writes):
+                          block_table, page_size, k_pages, v_pages, writes, layout="half", unit_norm_after=False,
+                          values_are_keys=False):
         """From the 32-bit rows [q | k | v]: optional per-head RMS norm of q and k (gains of ``dim``), rotation of the first
-        ``rot_dims`` elements of every q and k head by position * freq32, queries into ``q_out`` in the storage type, and
-        with ``writes`` keys and values into their pages."""
+        ``rot_dims`` elements of every q and k head by position * freq32 (``layout`` 'half': element i with i + rot_dims/2;
+        'interleaved': 2i with 2i + 1), with ``unit_norm_after`` every q and k head divided by its root mean square after
+        the rotation (no gain), queries into ``q_out`` in the storage type, and with ``writes`` keys and values into their
+        pages. With ``values_are_keys`` the rows are [q | k] and a value head is the key head as projected."""
         self._rows(qkv32, torch.float32, "attention_prepare qkv"); _need(q_out, None, "attention_prepare q")
         m = qkv32.shape[0]
-        if qkv32.shape[1] != (heads + kv_heads) * dim + kv_heads * vdim or tuple(q_out.shape) != (m, heads * dim):
+        if qkv32.shape[1] != (heads + kv_heads) * dim + (0 if values_are_keys else kv_heads * vdim) or tuple(q_out.shape) != (m, heads * dim) \
+                or (values_are_keys and vdim != dim):
             raise KernelError("attention_prepare: widths do not fit the head counts")
+        flags = {"half": 0, "interleaved": 1}[layout] | (2 if unit_norm_after else 0) | (4 if values_are_keys else 0)
         for t in (q_gain32, k_gain32):
             if t is not None:
                 _need(t, torch.float32, "attention_prepare gain")
@@ -867,7 +934,7 @@ class Kernels:
             _ptr(qkv32), c_int(qkv32.stride(0)), _ptr(q_out), _ptr(q_gain32), _ptr(k_gain32), c_float(eps), _ptr(freq32 if rot_dims else None),
             c_int(rot_dims), _ptr(ctx.positions), _ptr(ctx.req_index), _ptr(block_table if writes else None), c_int(bt_stride), c_int(page_size),
             _ptr(k_pages if writes else None), _ptr(v_pages if writes else None), c_int(num_pages), c_int(m), c_int(heads), c_int(kv_heads),
-            c_int(dim), c_int(vdim), c_int(1 if writes else 0), c_int(_DT[q_out.dtype]), self._stream()), "attention_prepare")
+            c_int(dim), c_int(vdim), c_int(1 if writes else 0), c_int(_DT[q_out.dtype]), c_int(flags), self._stream()), "attention_prepare")
 
     def attention_flex(self, q, out, heads, kv_heads, dim, vdim, scale, softcap, slopes32, window, chunk, out_scale, ctx,
                        block_table, page_size, k_pages, v_pages):
@@ -967,8 +1034,9 @@ class Kernels:
             c_int(ctx.host.num_requests), c_int(width), c_int(taps), c_int(blocks), c_int(_DT[out.dtype]), self._stream()), "rglru_scan")
 
     # ---- attention through a latent (latent_attention.cu) -------------------------------------------
-    def latent_store(self, z32, gain32, eps, freq32, mag, ctx, block_table, page_size, pages, rank, rot):
-        """Cache rows [rms-normed z[:, :rank] * gain | z[:, rank:] rotated in interleaved pairs by position * freq32]."""
+    def latent_store(self, z32, gain32, eps, freq32, mag, ctx, block_table, page_size, pages, rank, rot, layout="interleaved"):
+        """Cache rows [rms-normed z[:, :rank] * gain | z[:, rank:] rotated by position * freq32]; ``layout`` 'interleaved':
+        pairs (2i, 2i + 1), 'half': pairs (i, i + rot/2)."""
         self._rows(z32, torch.float32, "latent_store z"); _need(gain32, torch.float32, "latent_store gain"); _need(freq32, torch.float32, "latent_store freq")
         _need(pages, None, "latent_store pages"); _need(block_table, torch.int32, "block_table", contiguous=False)
         if z32.shape[1] != rank + rot or tuple(pages.shape[1:]) != (1, page_size, rank + rot) or freq32.numel() != rot // 2 \
@@ -977,7 +1045,8 @@ class Kernels:
         self._check(self._lib.nib_latent_store(
             _ptr(z32), c_int(z32.stride(0)), _ptr(gain32), c_float(eps), _ptr(freq32), c_float(mag), _ptr(ctx.positions),
             _ptr(ctx.req_index), _ptr(block_table), c_int(block_table.stride(0)), c_int(page_size), _ptr(pages),
-            c_int(pages.shape[0]), c_int(z32.shape[0]), c_int(rank), c_int(rot), c_int(_DT[pages.dtype]), self._stream()), "latent_store")
+            c_int(pages.shape[0]), c_int(z32.shape[0]), c_int(rank), c_int(rot), c_int(_DT[pages.dtype]), c_int(_LAYOUT[layout]),
+            self._stream()), "latent_store")
 
     def _latent_mma(self, dtype, rank, rot) -> bool:
         """Whether the tensor-core kernels run the attention over rows of ``rank + rot`` elements of ``dtype``."""
@@ -992,9 +1061,10 @@ class Kernels:
             return self._lib.nib_latent_attention_mma_qwidth(c_int(rank), c_int(rot)), torch.bfloat16
         return rank + rot, torch.float32
 
-    def latent_query(self, q32, w_uk, freq32, mag, positions, qa, heads, dn, rank, rot):
+    def latent_query(self, q32, w_uk, freq32, mag, positions, qa, heads, dn, rank, rot, layout="interleaved"):
         """qa[t, h] = [W_uk,h^T q32[t, h, :dn] | q32[t, h, dn:] rotated | zeros]; w_uk: [heads * dn, rank] as stored;
-        qa: [tokens, heads * width] in the layout ``latent_query_layout`` gives."""
+        qa: [tokens, heads * width] in the layout ``latent_query_layout`` gives; ``layout``: the rotated pairs, as in
+        ``latent_store``."""
         self._rows(q32, torch.float32, "latent_query q"); _need(w_uk, None, "latent_query w_uk"); _need(qa, None, "latent_query qa")
         _need(freq32, torch.float32, "latent_query freq")
         m = q32.shape[0]
@@ -1008,17 +1078,22 @@ class Kernels:
             # round trip to memory each: 40-80 us for the 8 tokens of a decode step at heads of 128)
             self._check(self._lib.nib_head_product_kn(_ptr(q32), c_int(q32.stride(0)), _ptr(w_uk), _ptr(freq32), c_float(mag), _ptr(positions),
                                                       _ptr(qa), c_int(ldq), c_int(m), c_int(heads), c_int(rank), c_int(dn), c_int(rot),
-                                                      self._stream()), "latent_query (tensor cores)")
+                                                      c_int(_LAYOUT[layout]), self._stream()), "latent_query (tensor cores)")
             return
         self._check(self._lib.nib_latent_query(_ptr(q32), c_int(q32.stride(0)), _ptr(w_uk), _ptr(freq32), c_float(mag), _ptr(positions),
                                                _ptr(qa), c_int(ldq), c_int(_DT[qa.dtype]), c_int(m), c_int(heads), c_int(dn), c_int(rank),
-                                               c_int(rot), c_int(_DT[w_uk.dtype]), self._stream()), "latent_query")
+                                               c_int(rot), c_int(_DT[w_uk.dtype]), c_int(_LAYOUT[layout]), self._stream()), "latent_query")
 
-    def latent_attention(self, qa, lat32, ctx, block_table, page_size, pages, heads, rank, rot, scale, window):
+    def latent_attention(self, qa, lat32, ctx, block_table, page_size, pages, heads, rank, rot, scale, window, sink32=None):
         """lat32[t, h] = sum_j softmax_j((qa[t, h] . row_j) * scale) * row_j[:rank] over the cached rows of the token's
         request at positions lo..own (lo = own - window + 1 with a window). bfloat16 rows of a supported width run on
         the tensor cores: the leading requests that bring one token each go to the decode kernel (keys split over
-        CTAs), the others to the kernel for prompt portions; everything else runs the general kernel."""
+        CTAs), the others to the kernel for prompt portions; everything else runs the general kernel. ``sink32`` (one
+        number per head): exp(sink32[h]) is added to the softmax's denominator once, with no value behind it."""
+        if sink32 is not None:
+            _need(sink32, torch.float32, "latent_attention sink")
+            if sink32.numel() != heads:
+                raise KernelError("latent_attention: one sink per head")
         _need(qa, None, "latent_attention qa"); _need(lat32, torch.float32, "latent_attention out"); _need(pages, None, "latent_attention pages")
         _need(block_table, torch.int32, "block_table", contiguous=False)
         m = qa.shape[0]
@@ -1031,7 +1106,7 @@ class Kernels:
             self._check(self._lib.nib_latent_attention(
                 _ptr(qa), _ptr(lat32), _ptr(ctx.positions), _ptr(ctx.req_index), _ptr(block_table), c_int(bt_stride),
                 c_int(page_size), _ptr(pages), c_int(pages.shape[0]), c_int(m), c_int(heads), c_int(rank), c_int(rot), c_float(scale),
-                c_int(window), c_int(_DT[pages.dtype]), self._stream()), "latent_attention")
+                c_int(window), c_int(_DT[pages.dtype]), _ptr(sink32), self._stream()), "latent_attention")
             return
         q_lens, ctx_lens = ctx.host.q_lens, ctx.host.ctx_lens
         n_req = len(q_lens)
@@ -1052,7 +1127,7 @@ class Kernels:
             self._check(self._lib.nib_latent_attention_mma(
                 c_int(1), _ptr(qa), _ptr(lat32), _ptr(ctx.q_start), _ptr(ctx.ctx_lens), _ptr(block_table), c_int(bt_stride),
                 c_int(page_size), _ptr(pages), c_int(pages.shape[0]), c_int(n_dec), c_int(1), *tail, c_int(splits),
-                _ptr(part_o), _ptr(part_ml), self._stream()), "latent attention decode (mma)")
+                _ptr(part_o), _ptr(part_ml), _ptr(sink32), self._stream()), "latent attention decode (mma)")
             if splits > 1:
                 self.launches += 1
         if n_dec < n_req:
@@ -1061,10 +1136,16 @@ class Kernels:
                 c_int(0), _ptr(qa), _ptr(lat32), c_void_p(ctx.q_start.data_ptr() + 4 * n_dec), c_void_p(ctx.ctx_lens.data_ptr() + 4 * n_dec),
                 c_void_p(block_table.data_ptr() + 4 * n_dec * bt_stride), c_int(bt_stride), c_int(page_size), _ptr(pages),
                 c_int(pages.shape[0]), c_int(n_req - n_dec), c_int(max(q_lens[n_dec:])), *tail, c_int(1), _ptr(None), _ptr(None),
-                self._stream()), "latent attention prefill (mma)")
+                _ptr(sink32), self._stream()), "latent attention prefill (mma)")
 
-    def latent_value(self, lat32, w_uv, out, heads, dv, rank):
-        """out[t, h*dv + j] = w_uv[h*dv + j, :] . lat32[t, h, :]."""
+    def latent_value(self, lat32, w_uv, out, heads, dv, rank, gate32=None):
+        """out[t, h*dv + j] = w_uv[h*dv + j, :] . lat32[t, h, :], times sigmoid(gate32[t, h*dv + j]) with a gate."""
+        ldg = 0
+        if gate32 is not None:
+            self._rows(gate32, torch.float32, "latent_value gate")
+            if tuple(gate32.shape) != (lat32.shape[0], heads * dv):
+                raise KernelError("latent_value: the gate has the output's shape")
+            ldg = gate32.stride(0)
         _need(lat32, torch.float32, "latent_value lat"); _need(w_uv, None, "latent_value w_uv"); self._rows(out, w_uv.dtype, "latent_value out")
         m = lat32.shape[0]
         if tuple(lat32.shape) != (m, heads * rank) or tuple(w_uv.shape) != (heads * dv, rank) or tuple(out.shape) != (m, heads * dv):
@@ -1072,11 +1153,11 @@ class Kernels:
         if w_uv.dtype == torch.bfloat16 and not self.options.force_simt_gemm \
                 and self._lib.nib_head_product_supported(c_int(0), c_int(rank), c_int(dv)) == 1:
             self._check(self._lib.nib_head_product_nk(_ptr(lat32), c_int(lat32.stride(0)), _ptr(w_uv), _ptr(None), _ptr(out), c_int(out.stride(0)),
-                                                      c_longlong(dv), c_int(0), c_int(m), c_int(heads), c_int(dv), c_int(rank), self._stream()),
-                        "latent_value (tensor cores)")
+                                                      c_longlong(dv), c_int(0), c_int(m), c_int(heads), c_int(dv), c_int(rank), _ptr(gate32), c_int(ldg),
+                                                      self._stream()), "latent_value (tensor cores)")
             return
         self._check(self._lib.nib_latent_value(_ptr(lat32), _ptr(w_uv), _ptr(out), c_int(out.stride(0)), c_int(m), c_int(heads),
-                                               c_int(dv), c_int(rank), c_int(_DT[w_uv.dtype]), self._stream()), "latent_value")
+                                               c_int(dv), c_int(rank), c_int(_DT[w_uv.dtype]), _ptr(gate32), c_int(ldg), self._stream()), "latent_value")
 
     def argmax(self, logits, out):
         """First index of each row's maximum. Few rows of a large vocabulary are cut into pieces for many CTAs."""

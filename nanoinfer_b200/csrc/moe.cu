@@ -1,0 +1,272 @@
+// Routed experts: every token goes through `top` of `experts` small gated feed-forwards, chosen by a router.
+//
+//  * moe_route: from the 32-bit router logits z [tokens, experts]: the `top` largest (the first of equal ones), and
+//    for each its weight sigmoid(z) (not renormalized). One warp per token.
+//  * moe_group: the (token, choice) entries ordered by expert: row_of[entry] = its row in that order, src_of[row] = the
+//    entry, and a table of row tiles (expert, first row, rows), none of which spans two experts. One block; the table's
+//    length depends on the routing, so the products below are launched with the largest grid the sizes allow and a
+//    block without a tile leaves at once: the launches never depend on the batch's content.
+//  * moe_gemm (CUDA cores; any sizes, float or bfloat16): per tile, rows gathered through src_of:
+//      gate/up:  act[row] = silu(w g) * (w u),  g = W_gate,e h, u = W_up,e h,  w = the entry's weight
+//                (the weight stands on the expert's INPUT; W (w h) = w (W h), so it is applied in 32-bit to the products),
+//      down:     y[row] = W_down,e act[row] as floats; with one choice per token straight into the token's output row.
+//    Every output element is accumulated by one thread over ascending k: a row's result depends on the row alone.
+//  * moe_combine: out[t] += sum over the token's choices, in ascending order of choice, of y[row_of[t, choice]].
+#include "common.cuh"
+#include <climits>
+
+constexpr int MOE_MAX_EXPERTS = 1024;
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ z, int ldz, int* __restrict__ sel_e, float* __restrict__ sel_w, int tokens, int experts, int top) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= tokens) return;
+    const float* zr = z + (size_t)t * ldz;
+    unsigned taken = 0;     // bit j: this lane's expert lane + 32 j is chosen already
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int bi = INT_MAX;
+        for (int j = 0; lane + 32 * j < experts; ++j) {
+            if ((taken >> j) & 1u) continue;
+            const int e = lane + 32 * j;
+            const float v = zr[e];
+            if (bi == INT_MAX || v > best) { best = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != INT_MAX && (bi == INT_MAX || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
+        }
+        if (bi == INT_MAX) bi = 0;
+        if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+        if (lane == 0) {
+            sel_e[(size_t)t * top + k] = bi;
+            sel_w[(size_t)t * top + k] = 1.0f / (1.0f + expf(-best));
+        }
+    }
+}
+
+// tiles: [max_tiles, 3] = (expert, first row, rows); n_tiles[0] = how many are in use.
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int* __restrict__ sel_e, int n, int experts, int tile_rows, int* __restrict__ row_of, int* __restrict__ src_of,
+                 int* __restrict__ tiles, int* __restrict__ n_tiles, int max_tiles) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
+    __shared__ int cnt[MOE_MAX_EXPERTS], off[MOE_MAX_EXPERTS], toff[MOE_MAX_EXPERTS], cur[MOE_MAX_EXPERTS];
+    const int tid = threadIdx.x, lane = tid & 31;
+    for (int e = tid; e < experts; e += blockDim.x) { cnt[e] = 0; cur[e] = 0; }
+    __syncthreads();
+    for (int i = tid; i < n; i += blockDim.x) atomicAdd(&cnt[sel_e[i]], 1);
+    __syncthreads();
+    if (tid < 32) {     // exclusive sums of the rows and of the tiles, 32 experts at a time
+        int run = 0, trun = 0;
+        for (int base = 0; base < experts; base += 32) {
+            const int c = base + lane < experts ? cnt[base + lane] : 0;
+            const int tl = (c + tile_rows - 1) / tile_rows;
+            int ic = c, it = tl;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int a = __shfl_up_sync(0xffffffffu, ic, o), b = __shfl_up_sync(0xffffffffu, it, o);
+                if (lane >= o) { ic += a; it += b; }
+            }
+            if (base + lane < experts) { off[base + lane] = run + ic - c; toff[base + lane] = trun + it - tl; }
+            run += __shfl_sync(0xffffffffu, ic, 31);
+            trun += __shfl_sync(0xffffffffu, it, 31);
+        }
+        if (lane == 0) n_tiles[0] = min(trun, max_tiles);
+    }
+    __syncthreads();
+    for (int e = tid; e < experts; e += blockDim.x) {
+        const int c = cnt[e];
+        for (int j = 0; j * tile_rows < c; ++j) {
+            const int ti = toff[e] + j;
+            if (ti < max_tiles) {
+                tiles[3 * ti] = e;
+                tiles[3 * ti + 1] = off[e] + j * tile_rows;
+                tiles[3 * ti + 2] = min(tile_rows, c - j * tile_rows);
+            }
+        }
+    }
+    for (int i = tid; i < n; i += blockDim.x) {
+        const int e = sel_e[i];
+        const int pos = off[e] + atomicAdd(&cur[e], 1);
+        row_of[i] = pos;
+        src_of[pos] = i;
+    }
+}
+
+template <typename T, bool GATE_UP>
+__global__ void __launch_bounds__(256)
+moe_gemm_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, void* __restrict__ out, int ldo,
+                     const int* __restrict__ tiles, const int* __restrict__ n_tiles, const int* __restrict__ src_of,
+                     const float* __restrict__ sel_w, int top, int N, int K, int scatter) {
+    constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
+    if ((int)blockIdx.y >= n_tiles[0]) return;
+    __shared__ float As[BK][BM + 1];
+    __shared__ float Ws[BK][BN + 1];
+    __shared__ float Us[GATE_UP ? BK : 1][GATE_UP ? BN + 1 : 1];
+    __shared__ int a_row[BM];       // the activation row each of the tile's rows reads
+    __shared__ int o_row[BM];       // the row it writes
+    __shared__ float a_wgt[BM];
+    const int tid = threadIdx.x;
+    const int tx = tid % 16, ty = tid / 16;
+    const int expert = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+    const int n0 = blockIdx.x * BN;
+    const T* We = W + (size_t)expert * (GATE_UP ? 2 : 1) * N * K;
+    if (tid < BM) {
+        const int p = row0 + tid;
+        int ar = -1, orow = -1;
+        float wg = 0.f;
+        if (tid < rows) {
+            const int entry = src_of[p];
+            ar = GATE_UP ? entry / top : p;
+            orow = (!GATE_UP && scatter) ? entry / top : p;
+            wg = sel_w[entry];
+        }
+        a_row[tid] = ar; o_row[tid] = orow; a_wgt[tid] = wg;
+    }
+    __syncthreads();
+
+    float acc[TM][TN], acc2[GATE_UP ? TM : 1][GATE_UP ? TN : 1];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+    if (GATE_UP) {
+#pragma unroll
+        for (int i = 0; i < (GATE_UP ? TM : 1); ++i)
+#pragma unroll
+            for (int j = 0; j < (GATE_UP ? TN : 1); ++j) acc2[i][j] = 0.f;
+    }
+    for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int e = tid + i * 256;
+            const int r = e / BK, kk = e % BK;
+            const int gk = k0 + kk;
+            float a = 0.f, w = 0.f, u = 0.f;
+            if (gk < K) {
+                if (a_row[r] >= 0) a = Elem<T>::load(A + (size_t)a_row[r] * lda + gk);
+                if (n0 + r < N) {
+                    w = Elem<T>::load(We + (size_t)(n0 + r) * K + gk);
+                    if (GATE_UP) u = Elem<T>::load(We + (size_t)(N + n0 + r) * K + gk);
+                }
+            }
+            As[kk][r] = a;
+            Ws[kk][r] = w;
+            if (GATE_UP) Us[kk][r] = u;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[TM], w[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) w[j] = Ws[kk][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+            if (GATE_UP) {
+                float u[TN];
+#pragma unroll
+                for (int j = 0; j < TN; ++j) u[j] = Us[kk][tx * TN + j];
+#pragma unroll
+                for (int i = 0; i < (GATE_UP ? TM : 1); ++i)
+#pragma unroll
+                    for (int j = 0; j < (GATE_UP ? TN : 1); ++j) acc2[i][j] = fmaf(a[i], u[j], acc2[i][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int r = ty * TM + i;
+        if (r >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + tx * TN + j;
+            if (n >= N) continue;
+            const size_t o = (size_t)o_row[r] * ldo + n;
+            if (GATE_UP) {
+                const float g = acc[i][j] * a_wgt[r], u = acc2[GATE_UP ? i : 0][GATE_UP ? j : 0] * a_wgt[r];
+                Elem<T>::store((T*)out + o, g / (1.0f + expf(-g)) * u);
+            } else if (scatter) {
+                ((float*)out)[o] += acc[i][j];
+            } else {
+                ((float*)out)[o] = acc[i][j];
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of, float* __restrict__ out, int tokens, int width, int top) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)tokens * width) return;
+    const int t = (int)(i / width), c = (int)(i % width);
+    float acc = out[i];
+    for (int k = 0; k < top; ++k) acc += y[(size_t)row_of[(size_t)t * top + k] * width + c];
+    out[i] = acc;
+}
+
+NIB_API int nib_moe_route(const float* z, int ldz, int* sel_e, float* sel_w, int tokens, int experts, int top, cudaStream_t stream) {
+    NIB_REQUIRE(tokens >= 0 && experts > 0 && experts <= MOE_MAX_EXPERTS && top > 0 && top <= experts,
+                "moe_route: %d experts (up to %d), %d chosen", experts, MOE_MAX_EXPERTS, top);
+    if (tokens == 0) return 0;
+    NIB_CUDA(launch_pdl(moe_route_kernel, dim3(ceil_div(tokens, 4)), dim3(128), (size_t)0, stream, z, ldz, sel_e, sel_w, tokens, experts, top));
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+// The largest number of tiles that `entries` rows in `experts` groups can make.
+NIB_API int nib_moe_max_tiles(int entries, int experts, int tile_rows) {
+    const long long by_rows = (entries + tile_rows - 1) / tile_rows + experts;
+    return (int)(by_rows < entries ? by_rows : entries);
+}
+
+NIB_API int nib_moe_group(const int* sel_e, int entries, int experts, int tile_rows, int* row_of, int* src_of, int* tiles, int* n_tiles,
+                          int max_tiles, cudaStream_t stream) {
+    NIB_REQUIRE(entries >= 0 && experts > 0 && experts <= MOE_MAX_EXPERTS && tile_rows > 0 && max_tiles >= nib_moe_max_tiles(entries, experts, tile_rows),
+                "moe_group: bad sizes");
+    if (entries == 0) return 0;
+    NIB_CUDA(launch_pdl(moe_group_kernel, dim3(1), dim3(1024), (size_t)0, stream, sel_e, entries, experts, tile_rows, row_of, src_of, tiles, n_tiles, max_tiles));
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+// gate_up != 0: A = the tokens' activations [tokens, K] (rows gathered through src_of), W [experts, 2N, K] (gate rows, then
+// up rows), out [entries, N] in the storage type. Else: A = [entries, K] in the grouped order, W [experts, N, K], out floats:
+// [entries, N] in the grouped order, or with scatter (one choice per token) added into the token's row of [tokens, N].
+// The tiles must have been made for rows of 64.
+NIB_API int nib_moe_gemm_simt(int gate_up, const void* A, int lda, const void* W, void* out, int ldo, const int* tiles, const int* n_tiles,
+                              int max_tiles, const int* src_of, const float* sel_w, int top, int N, int K, int scatter, int dtype,
+                              cudaStream_t stream) {
+    NIB_REQUIRE(N > 0 && K > 0 && top > 0 && max_tiles >= 0 && (!scatter || top == 1), "moe_gemm: bad sizes");
+    NIB_REQUIRE(dtype == NIB_F32 || dtype == NIB_BF16, "moe_gemm: unknown dtype %d", dtype);
+    if (max_tiles == 0) return 0;
+    const dim3 grid(ceil_div(N, 64), max_tiles), block(256);
+#define NIB_MG(T, GU) \
+    NIB_CUDA(launch_pdl(moe_gemm_simt_kernel<T, GU>, grid, block, (size_t)0, stream, (const T*)A, lda, (const T*)W, out, ldo, tiles, n_tiles, src_of, sel_w, top, N, K, scatter))
+    if (dtype == NIB_F32) { if (gate_up) NIB_MG(float, true); else NIB_MG(float, false); }
+    else { if (gate_up) NIB_MG(__nv_bfloat16, true); else NIB_MG(__nv_bfloat16, false); }
+#undef NIB_MG
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+NIB_API int nib_moe_combine(const float* y, const int* row_of, float* out, int tokens, int width, int top, cudaStream_t stream) {
+    NIB_REQUIRE(tokens >= 0 && width > 0 && top > 0, "moe_combine: bad sizes");
+    if (tokens == 0) return 0;
+    NIB_CUDA(launch_pdl(moe_combine_kernel, dim3(ceil_div((long long)tokens * width, 256)), dim3(256), (size_t)0, stream, y, row_of, out, tokens, width, top));
+    NIB_LAUNCH_CHECK();
+    return 0;
+}

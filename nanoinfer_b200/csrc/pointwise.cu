@@ -516,3 +516,58 @@ NIB_API int nib_gated_norm(const float* o, int ldo, const float* gate, int ldg, 
     NIB_LAUNCH_CHECK();
     return 0;
 }
+
+// ---------------------------------------------------------------------------------- norm of a branch's output, added
+// x[t] += mult * y[t] / sqrt(mean(y[t]^2) + eps) * gain: the residual sum of a block whose norm stands on the
+// sublayer's OUTPUT. With `h_out` the new x is also written in the storage type (what the next sublayer reads);
+// with `clear` y is left zeroed, ready for the next sublayer's products to add into. A block per row when rows are
+// few (a decode step), else a warp per row. All arithmetic is 32-bit.
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_add_kernel(float* __restrict__ y, const float* __restrict__ gain, float* __restrict__ x, T* __restrict__ h_out,
+                   int rows, int width, float eps, float mult, int clear) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
+    __shared__ float part[THREADS / 32];
+    constexpr bool BLOCK_ROW = THREADS > 32 * 4;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = BLOCK_ROW ? blockIdx.x : blockIdx.x * (THREADS / 32) + warp;
+    if (row >= rows) return;        // a whole block (block per row) or a whole warp (warp per row) leaves together
+    const int first = BLOCK_ROW ? threadIdx.x : lane, step = BLOCK_ROW ? THREADS : 32;
+    float* yr = y + (size_t)row * width;
+    float* xr = x + (size_t)row * width;
+    float ss = 0.f;
+    for (int c = first; c < width; c += step) ss = fmaf(yr[c], yr[c], ss);
+    ss = warp_sum(ss);
+    if (BLOCK_ROW) {
+        if (lane == 0) part[warp] = ss;
+        __syncthreads();
+        ss = 0.f;
+        for (int w = 0; w < THREADS / 32; ++w) ss += part[w];      // the same order in every thread
+    }
+    const float scale = mult / sqrtf(ss / (float)width + eps);
+    for (int c = first; c < width; c += step) {
+        const float v = xr[c] + yr[c] * scale * gain[c];
+        xr[c] = v;
+        if (h_out != nullptr) Elem<T>::store(h_out + (size_t)row * width + c, v);
+        if (clear) yr[c] = 0.f;
+    }
+}
+
+NIB_API int nib_rmsnorm_add(float* y, const float* gain, float* x, void* h_out, int rows, int width, float eps, float mult,
+                            int clear, int dtype, cudaStream_t stream) {
+    NIB_REQUIRE(rows >= 0 && width > 0, "rmsnorm_add: bad sizes");
+    NIB_REQUIRE(dtype == NIB_F32 || dtype == NIB_BF16, "rmsnorm_add: unknown dtype %d", dtype);
+    if (rows == 0) return 0;
+    const bool block_row = rows <= 64 && width >= 512;
+#define NIB_RA(T, THREADS, GRID) \
+    NIB_CUDA(launch_pdl(rmsnorm_add_kernel<T, THREADS>, dim3(GRID), dim3(THREADS), (size_t)0, stream, y, gain, x, (T*)h_out, rows, width, eps, mult, clear))
+    if (block_row) {
+        if (dtype == NIB_F32) NIB_RA(float, 256, rows); else NIB_RA(__nv_bfloat16, 256, rows);
+    } else {
+        if (dtype == NIB_F32) NIB_RA(float, 128, ceil_div(rows, 4)); else NIB_RA(__nv_bfloat16, 128, ceil_div(rows, 4));
+    }
+#undef NIB_RA
+    NIB_LAUNCH_CHECK();
+    return 0;
+}

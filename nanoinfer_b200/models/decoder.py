@@ -38,7 +38,7 @@ class DecoderModel:
                 bind = getattr(part, "bind_positions", None)
                 if bind is not None:
                     bind(self.positions)
-            self.layers.append(get_arrangement(layer.arrangement)(parts))
+            self.layers.append(get_arrangement(layer.arrangement)(parts, **layer.params))
         self.final_norm = _build_part(plan.final_norm, tensors, shared)
         self.head = _build_part(plan.lm_head, tensors, shared)
         self.schedule = list(plan.schedule)

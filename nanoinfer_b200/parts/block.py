@@ -3,6 +3,9 @@
 ``parallel``: ``x += mixer(norm_a(x)) + feed_forward(norm_b(x))``, both of the same x, optionally followed by a mix
 with the step's earlier streams.
 
+``output_norm``: ``x += mult * norm(mixer(x)); x += mult * norm(feed_forward(x))``: the norms stand on the branches'
+outputs, the branches read the stream as it is.
+
 ``pre_norm``: ``x += mixer(norm(x)); x += feed_forward(norm(x))`` with a norm of its own before each
 (cpp/src/model.cpp:364-400, nanoinfer/layers.py:328-339). The residual stream ``x`` is 32-bit and
 both sums are made in 32-bit inside the projections that produce the addends.
@@ -73,5 +76,47 @@ class ParallelBlock:
             self.depth.forward(x32, ctx)
 
 
+class OutputNormBlock:
+    """``x <- x + mult * norm_a(mixer(x))``, then ``x <- x + mult * norm_b(feed_forward(x))``: the branches read the stream
+    itself (in the compute dtype), and each norm stands on its branch's output. parts: ``mixer``, ``mixer_norm`` and
+    optionally ``ffn`` with ``ffn_norm``; ``mult``: the factor on what a branch adds. The norms offer
+    ``add_normed(y32, x32, mult, h_out, clear)``.
+
+    A branch adds its result into a zeroed 32-bit buffer as it would into the stream (sums over K splits and over experts
+    included); the norm's kernel reads that buffer, adds to the stream, writes the stream's rounding for the next branch
+    and leaves the buffer zeroed: one pass per branch. The buffer and the rounded stream live in the step's scratch, so
+    that consecutive layers of this arrangement share them (the layer before has left both ready)."""
+
+    part_names = ("mixer", "mixer_norm", "ffn", "ffn_norm")
+    _SCRATCH = "output_norm.buffers"
+
+    def __init__(self, parts: Dict[str, object], mult: float = 1.0):
+        self.mixer, self.mixer_norm = parts["mixer"], parts["mixer_norm"]
+        self.ffn, self.ffn_norm = parts.get("ffn"), parts.get("ffn_norm")
+        if (self.ffn is None) != (self.ffn_norm is None):
+            raise ValueError("a feed-forward and the norm on its output come together")
+        self.mult = float(mult)
+        self.part_names = tuple(n for n in OutputNormBlock.part_names if parts.get(n) is not None)
+
+    def forward(self, x32: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
+        rt = self.mixer.rt
+        same = rt.dtype == torch.float32        # the branches then read the stream itself
+        held = ctx.scratch.get(self._SCRATCH)
+        if held is None or held[0] is not x32:
+            y32 = torch.zeros_like(x32)
+            h = x32 if same else torch.empty(x32.shape, dtype=rt.dtype, device=x32.device)
+            if not same:
+                rt.ops.unary(x32, h, "copy")
+            held = (x32, y32, h)
+            ctx.scratch[self._SCRATCH] = held
+        _, y32, h = held
+        self.mixer.forward(h, y32, ctx, cache)
+        self.mixer_norm.add_normed(y32, x32, self.mult, None if same else h, clear=True)
+        if self.ffn is not None:
+            self.ffn.forward(h, y32, ctx)
+            self.ffn_norm.add_normed(y32, x32, self.mult, None if same else h, clear=True)
+
+
 register_arrangement("pre_norm", PreNormBlock)
+register_arrangement("output_norm", OutputNormBlock)
 register_arrangement("parallel", ParallelBlock)

@@ -10,7 +10,7 @@ from typing import Dict
 import torch
 
 from ..registry import register_part
-from .base import FeedForward, Runtime, StepContext
+from .base import FeedForward, Runtime, StepContext, as_tensor
 from .spec import PartSpec, TensorSpec
 
 
@@ -79,5 +79,51 @@ class PolyNormFeedForward(FeedForward):
         self.ops.linear(act, self.w_down, self.b_down, residual32, "add")
 
 
+class RoutedExperts(FeedForward):
+    """A mixture of experts: ``experts`` gated feed-forwards ``W_down (silu(W_gate x) * (W_up x))`` without biases, of
+    which every token uses ``top``. Router: logits ``z = W_router h`` in 32-bit, scores ``sigmoid(z)``; the ``top`` largest
+    are chosen (the first of equal ones); a chosen expert's score is its weight, as it is (``renormalize`` is not among
+    the options), and it multiplies the expert's INPUT: the output is ``sum_e expert_e(score_e * h)``, added to the
+    residual stream.
+
+    params: ``hidden``, ``ff`` (an expert's inner width), ``experts``, ``top``. tensors: ``router [experts, hidden]`` and per
+    expert i ``e<i>_gate, e<i>_up [ff, hidden]``, ``e<i>_down [hidden, ff]``; they are stacked once at load into
+    ``[experts, 2 ff, hidden]`` (gate rows, then up rows) and ``[experts, hidden, ff]``."""
+
+    graph_safe = True   # the launches depend on the token count alone: the tile table of the routing lives on the device
+
+    @staticmethod
+    def spec(prefix: str, hidden: int, ff: int, experts: int, top: int) -> PartSpec:
+        t = {"router": TensorSpec(f"{prefix}.router", (experts, hidden))}
+        for i in range(experts):
+            t[f"e{i}_gate"] = TensorSpec(f"{prefix}.e{i}.gate", (ff, hidden))
+            t[f"e{i}_up"] = TensorSpec(f"{prefix}.e{i}.up", (ff, hidden))
+            t[f"e{i}_down"] = TensorSpec(f"{prefix}.e{i}.down", (hidden, ff))
+        return PartSpec("routed_experts", {"hidden": hidden, "ff": ff, "experts": experts, "top": top}, t)
+
+    def __init__(self, spec: PartSpec, tensors: Dict[str, torch.Tensor], rt: Runtime):
+        super().__init__(spec, tensors, rt)
+        p = spec.params
+        self.hidden, self.ff = int(p["hidden"]), int(p["ff"])
+        self.experts, self.top = int(p["experts"]), int(p["top"])
+        if not (1 <= self.top <= self.experts):
+            raise ValueError(f"a token uses {self.top} of {self.experts} experts")
+        self.w_router = rt.matrix(tensors["router"])
+        self.w_gate_up = rt.matrix(torch.stack([torch.cat([tensors[f"e{i}_gate"], tensors[f"e{i}_up"]], dim=0)
+                                                for i in range(self.experts)]))
+        self.w_down = rt.matrix(torch.stack([tensors[f"e{i}_down"] for i in range(self.experts)]))
+
+    def forward(self, h, residual32: torch.Tensor, ctx: StepContext) -> None:
+        h = as_tensor(h)
+        m, dev = h.shape[0], h.device
+        z32 = torch.empty((m, self.experts), dtype=torch.float32, device=dev)
+        self.ops.linear(h, self.w_router, None, z32, "f32")
+        chosen = torch.empty((m, self.top), dtype=torch.int32, device=dev)
+        weight = torch.empty((m, self.top), dtype=torch.float32, device=dev)
+        self.ops.moe_route(z32, self.top, chosen, weight)
+        self.ops.moe_experts(h, chosen, weight, self.w_gate_up, self.w_down, residual32)
+
+
+register_part("routed_experts", RoutedExperts)
 register_part("swiglu", SwiGLU)
 register_part("polynorm_ffn", PolyNormFeedForward)

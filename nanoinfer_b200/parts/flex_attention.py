@@ -9,7 +9,11 @@ With ``q = W_q h + b_q`` (likewise k, v), in this order:
 * ``qk_norm``: every head of q and k is divided by its root mean square (``eps`` inside the root) and multiplied by a
   gain of the head's size that all heads share;
 * ``rot`` = (dims, base): the first ``dims`` elements of every q and k head are turned by ``position * base^(-2i/dims)``,
-  element i paired with i + dims/2; the angle is formed in 32-bit;
+  element i paired with i + dims/2 (``rot_layout`` "half") or 2i with 2i + 1 ("interleaved"); with ``rot_factor`` f
+  every frequency is divided by f (linear position scaling); the angle is formed in 32-bit;
+* ``unit_norm_after_rot``: every head of q and k is divided by its root mean square AFTER the rotation, no gain;
+* ``values_from_keys``: there is no value projection; a value head is the key head as projected, before norm and
+  rotation (``vdim`` = ``dim``);
 * ``score = (q . k) * scale``; with ``softcap`` c: ``c tanh(score / c)``; with ``slope_span`` s: head h of H loses
   ``2^(-s (h + 1) / H) * (i - j)`` at distance i - j;
 * position i sees j <= i; with ``window`` w only j > i - w; with ``chunk`` c only ``floor(j / c) == floor(i / c)``,
@@ -30,17 +34,17 @@ from .base import CacheNeed, LayerCache, Mixer, PagedTensor, Runtime, StateNeed,
 from .spec import PartSpec, TensorSpec
 
 
-def rotary_frequencies(dims: int, base: float) -> torch.Tensor:
-    """``base^(-2i/dims)`` for the ``dims/2`` pairs, computed in 64-bit and rounded to 32-bit once."""
+def rotary_frequencies(dims: int, base: float, factor: float = 1.0) -> torch.Tensor:
+    """``base^(-2i/dims) / factor`` for the ``dims/2`` pairs, computed in 64-bit and rounded to 32-bit once."""
     i = torch.arange(dims // 2, dtype=torch.float64)
-    return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / float(dims)).to(torch.float32)
+    return (torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / float(dims)) / float(factor)).to(torch.float32)
 
 
 class FlexAttention(Mixer):
     """params: ``hidden heads kv_heads dim vdim scale eps`` and the options ``bias`` (q, k, v), ``out_bias``, ``conv``
     (taps), ``qk_norm``, ``rot`` ((dims, base) or None), ``softcap``, ``slope_span``, ``window``, ``chunk``,
-    ``out_gate``, ``out_scale``. tensors: ``q k v o`` and, by option, ``q_b k_b v_b o_b q_conv k_conv v_conv
-    q_norm k_norm g``."""
+    ``out_gate``, ``out_scale``, ``rot_layout``, ``rot_factor``, ``unit_norm_after_rot``, ``values_from_keys``. tensors:
+    ``q k o``, ``v`` unless the values are the keys, and, by option, ``q_b k_b v_b o_b q_conv k_conv v_conv q_norm k_norm g``."""
 
     graph_safe = True   # launches do not depend on which requests are in the batch
 
@@ -48,17 +52,22 @@ class FlexAttention(Mixer):
     def spec(prefix: str, hidden: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, eps: float, *,
              bias: bool = False, out_bias: bool = False, conv: int = 0, qk_norm: bool = False, rot=None,
              softcap: float = 0.0, slope_span: float = 0.0, window: int = 0, chunk: int = 0, out_gate: bool = False,
-             out_scale: float = 1.0) -> PartSpec:
+             out_scale: float = 1.0, rot_layout: str = "half", rot_factor: float = 1.0, unit_norm_after_rot: bool = False,
+             values_from_keys: bool = False) -> PartSpec:
         nq, nk, nv = heads * dim, kv_heads * dim, kv_heads * vdim
         t = {"q": TensorSpec(f"{prefix}.q", (nq, hidden)), "k": TensorSpec(f"{prefix}.k", (nk, hidden)),
              "v": TensorSpec(f"{prefix}.v", (nv, hidden)), "o": TensorSpec(f"{prefix}.o", (hidden, heads * vdim))}
+        projected = ("q", nq), ("k", nk), ("v", nv)
+        if values_from_keys:
+            del t["v"]
+            projected = projected[:2]
         if bias:
-            for name, n in (("q", nq), ("k", nk), ("v", nv)):
+            for name, n in projected:
                 t[name + "_b"] = TensorSpec(f"{prefix}.{name}.b", (n,), "bias")
         if out_bias:
             t["o_b"] = TensorSpec(f"{prefix}.o.b", (hidden,), "bias")
         if conv:
-            for name, n in (("q", nq), ("k", nk), ("v", nv)):
+            for name, n in projected:
                 t[name + "_conv"] = TensorSpec(f"{prefix}.{name}.conv", (n, conv), "unit")
         if qk_norm:
             t["q_norm"] = TensorSpec(f"{prefix}.q.norm", (dim,), "gain")
@@ -69,7 +78,8 @@ class FlexAttention(Mixer):
                   "eps": float(eps), "bias": bias, "out_bias": out_bias, "conv": int(conv), "qk_norm": qk_norm,
                   "rot": None if rot is None else (int(rot[0]), float(rot[1])), "softcap": float(softcap),
                   "slope_span": float(slope_span), "window": int(window), "chunk": int(chunk), "out_gate": out_gate,
-                  "out_scale": float(out_scale)}
+                  "out_scale": float(out_scale), "rot_layout": str(rot_layout), "rot_factor": float(rot_factor),
+                  "unit_norm_after_rot": bool(unit_norm_after_rot), "values_from_keys": bool(values_from_keys)}
         return PartSpec("flex_attention", params, t)
 
     def __init__(self, spec: PartSpec, tensors: Dict[str, torch.Tensor], rt: Runtime):
@@ -83,25 +93,35 @@ class FlexAttention(Mixer):
         self.taps, self.softcap = int(p.get("conv", 0)), float(p.get("softcap", 0.0))
         self.window, self.chunk = int(p.get("window", 0)), int(p.get("chunk", 0))
         self.nq, self.nk, self.nv = self.heads * self.dim, self.kv_heads * self.dim, self.kv_heads * self.vdim
+        self.values_from_keys = bool(p.get("values_from_keys"))
+        if self.values_from_keys and (self.vdim != self.dim or self.taps):
+            raise ValueError("values that are the projected keys have the keys' width, and no convolution stands between")
+        if self.values_from_keys:
+            self.nv = 0
+        self.unit_norm_after = bool(p.get("unit_norm_after_rot"))
+        self.rot_layout = str(p.get("rot_layout", "half"))
+        if self.rot_layout not in ("half", "interleaved"):
+            raise ValueError(f"unknown layout of rotated pairs '{self.rot_layout}'")
         self.n_qkv = self.nq + self.nk + self.nv
         self.out_gate = bool(p.get("out_gate"))
         self.n_gate = self.heads * self.vdim if self.out_gate else 0
         # One product for everything that reads h: rows [q | k | v | gate]; the gate has no bias.
-        rows = [tensors["q"], tensors["k"], tensors["v"]] + ([tensors["g"]] if self.out_gate else [])
+        named = ("q", "k") if self.values_from_keys else ("q", "k", "v")
+        rows = [tensors[n] for n in named] + ([tensors["g"]] if self.out_gate else [])
         self.w_in = rt.matrix(torch.cat(rows, dim=0))
         self.b_in = None
         if p.get("bias"):
             b = torch.zeros(self.n_qkv + self.n_gate, dtype=torch.float32)
-            b[:self.n_qkv] = torch.cat([tensors["q_b"], tensors["k_b"], tensors["v_b"]]).to(torch.float32)
+            b[:self.n_qkv] = torch.cat([tensors[n + "_b"] for n in named]).to(torch.float32)
             self.b_in = rt.vector32(b)
-        self.conv_w = rt.vector32(torch.cat([tensors["q_conv"], tensors["k_conv"], tensors["v_conv"]], dim=0)) if self.taps else None
+        self.conv_w = rt.vector32(torch.cat([tensors[n + "_conv"] for n in named], dim=0)) if self.taps else None
         self.q_gain = rt.vector32(tensors["q_norm"]) if p.get("qk_norm") else None
         self.k_gain = rt.vector32(tensors["k_norm"]) if p.get("qk_norm") else None
         rot = p.get("rot")
         self.rot_dims = 0 if rot is None else int(rot[0])
         if self.rot_dims % 2 or self.rot_dims > self.dim:
             raise ValueError(f"rotated width {self.rot_dims} must be even and at most the head size {self.dim}")
-        self.freq = rotary_frequencies(self.rot_dims, float(rot[1])).to(rt.device) if self.rot_dims else None
+        self.freq = rotary_frequencies(self.rot_dims, float(rot[1]), float(p.get("rot_factor", 1.0))).to(rt.device) if self.rot_dims else None
         span = float(p.get("slope_span", 0.0))
         self.slopes = None
         if span:
@@ -114,6 +134,7 @@ class FlexAttention(Mixer):
     def cache_need(self) -> CacheNeed:
         # a chunk never looks further back than its own size, so pages behind it can go like a window's
         keep = self.window if self.window else self.chunk
+        # (values that are the projected keys are still cached beside the keys: the cached key is normed and rotated)
         return CacheNeed((PagedTensor("k", self.kv_heads, self.dim), PagedTensor("v", self.kv_heads, self.vdim)), keep)
 
     def state_need(self) -> Optional[StateNeed]:
@@ -133,7 +154,8 @@ class FlexAttention(Mixer):
         # norm, rotation, queries in the storage type, keys and values into their pages
         ops.attention_prepare(qkv32, q, self.heads, self.kv_heads, self.dim, self.vdim, self.q_gain, self.k_gain, self.eps,
                               self.freq, self.rot_dims, ctx, cache.block_table, cache.page_size, cache.pages["k"], cache.pages["v"],
-                              cache.writes)
+                              cache.writes, layout=self.rot_layout, unit_norm_after=self.unit_norm_after,
+                              values_are_keys=self.values_from_keys)
         gated = self.out_gate
         attn = torch.empty((m, self.heads * self.vdim), dtype=torch.float32 if gated else self.rt.dtype, device=dev)
         ops.attention_flex(q, attn, self.heads, self.kv_heads, self.dim, self.vdim, self.scale, self.softcap, self.slopes,

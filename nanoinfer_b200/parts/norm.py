@@ -43,6 +43,13 @@ class RMSNorm(Norm):
     def fold_into_projection(self, x32: torch.Tensor) -> Optional[FoldedNorm]:
         return FoldedNorm(x32, self.gain, self.eps, "rms")
 
+    def add_normed(self, y32: torch.Tensor, x32: torch.Tensor, mult: float = 1.0, h_out: Optional[torch.Tensor] = None,
+                   clear: bool = False) -> None:
+        """``x32 += mult * norm(y32)``: the norm stands on a branch's OUTPUT and its result goes into the stream. With
+        ``h_out`` the new stream is also written there in that tensor's type (what the next branch reads); with ``clear``
+        ``y32`` is left zeroed for the next branch to add into. One pass over the rows."""
+        self.ops.rmsnorm_add(y32, self.gain, self.eps, float(mult), x32, h_out, clear)
+
     def forward_with(self, other: "RMSNorm", x32: torch.Tensor):
         """``(self.forward(x32), other.forward(x32))`` with the rows read once: for blocks whose branches read the same
         stream through norms of their own. ``other`` must be an RMSNorm of the same size and eps."""

@@ -65,7 +65,8 @@ register_part("no_position", NoPositionEncoding)
 
 def scaled_frequencies(dims: int, base: float, scaling=None):
     """Frequencies of the ``dims/2`` rotated pairs, ``f_i = base^(-2i/dims)``, optionally rescaled the YaRN way, and
-    the factor on cos and sin. ``scaling`` = {factor, original, fast, slow}: a pair that turns more than ``fast``
+    the factor on cos and sin. ``scaling`` = {factor} alone: every frequency is divided by ``factor`` (linear scaling of
+    the positions), cos and sin as they are. ``scaling`` = {factor, original, fast, slow}: a pair that turns more than ``fast``
     times within ``original`` positions keeps its frequency, one that turns fewer than ``slow`` times has it divided
     by ``factor``, linearly blended in between over the pair index: with
     ``turn_dim(t) = dims * ln(original / (2 pi t)) / (2 ln base)``, ``lo = max(floor(turn_dim(fast)), 0)``,
@@ -77,6 +78,8 @@ def scaled_frequencies(dims: int, base: float, scaling=None):
     f = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / float(dims))
     if not scaling:
         return f, 1.0
+    if "original" not in scaling:
+        return f / float(scaling["factor"]), 1.0
     factor, original = float(scaling["factor"]), float(scaling["original"])
 
     def turn_dim(turns: float) -> float:
@@ -89,21 +92,28 @@ def scaled_frequencies(dims: int, base: float, scaling=None):
 
 class FrequencyRotary(PositionEncoding):
     """Rotary positions given as a vector of frequencies instead of tables: the kernels form
-    ``angle = position * frequency`` in 32-bit themselves, for any position, and rotate INTERLEAVED pairs
-    (element 2i with 2i + 1). params: ``dims`` (rotated width), ``base``, ``scaling`` (None or the dict of
-    ``scaled_frequencies``). No tensors. ``rotary()`` is None: mixers that want tables cannot bind to it."""
+    ``angle = position * frequency`` in 32-bit themselves, for any position, and rotate pairs in the ``layout``
+    "interleaved" (element 2i with 2i + 1; the default) or "half" (i with i + dims/2). params: ``dims`` (rotated width),
+    ``base``, ``scaling`` (None or a dict of ``scaled_frequencies``), ``layout``. No tensors. ``rotary()`` is None: mixers
+    that want tables cannot bind to it."""
 
     graph_safe = True   # launches do not depend on which requests are in the batch
 
     @staticmethod
-    def spec(dims: int, base: float, scaling=None) -> PartSpec:
-        return PartSpec("frequency_rotary", {"dims": dims, "base": base, "scaling": dict(scaling) if scaling else None})
+    def spec(dims: int, base: float, scaling=None, layout: str = "interleaved") -> PartSpec:
+        params = {"dims": dims, "base": base, "scaling": dict(scaling) if scaling else None}
+        if layout != "interleaved":
+            params["layout"] = layout
+        return PartSpec("frequency_rotary", params)
 
     def __init__(self, spec: PartSpec, tensors: Dict[str, torch.Tensor], rt: Runtime):
         super().__init__(spec, tensors, rt)
         self.dims = int(spec.params["dims"])
         if self.dims <= 0 or self.dims % 2:
             raise ValueError(f"rotated width must be positive and even, got {self.dims}")
+        self.layout = str(spec.params.get("layout", "interleaved"))
+        if self.layout not in ("interleaved", "half"):
+            raise ValueError(f"unknown layout of rotated pairs '{self.layout}'")
         f, self.magnitude = scaled_frequencies(self.dims, float(spec.params["base"]), spec.params.get("scaling"))
         self.freq = f.to(torch.float32).to(rt.device).contiguous()
 

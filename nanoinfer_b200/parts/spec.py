@@ -32,9 +32,11 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """A block: an arrangement (registry key) over named parts."""
+    """A block: an arrangement (registry key) over named parts, with the arrangement's own constants (``params``:
+    keyword arguments of its class, e.g. a factor on what a branch adds to the stream)."""
     arrangement: str
     parts: Dict[str, PartSpec]
+    params: Dict[str, object] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

@@ -100,3 +100,4 @@ def _ensure_builtin() -> None:
     from .models import qwen2 as _qwen2  # noqa: F401  registers Qwen2ForCausalLM
     from .models import nezalorn as _nezalorn  # noqa: F401  registers Nezalorn
     from .models import vafozen as _vafozen  # noqa: F401  registers Vafozen
+    from .models import darotar as _darotar  # noqa: F401  registers Darotar

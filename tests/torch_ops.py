@@ -134,12 +134,13 @@ class TorchOps:
 
     # ---- attention with options (attention_flex.cu) --------------------------------------------------
     def attention_prepare(self, qkv32, q_out, heads, kv_heads, dim, vdim, q_gain32, k_gain32, eps, freq32, rot_dims, ctx,
-                          block_table, page_size, k_pages, v_pages, writes):
+                          block_table, page_size, k_pages, v_pages, writes, layout="half", unit_norm_after=False,
+                          values_are_keys=False):
         m = qkv32.shape[0]
         nq, nk = heads * dim, kv_heads * dim
         q = qkv32[:, :nq].double().reshape(m, heads, dim)
         k = qkv32[:, nq:nq + nk].double().reshape(m, kv_heads, dim)
-        v = qkv32[:, nq + nk:].double().reshape(m, kv_heads, vdim)
+        v = k.clone() if values_are_keys else qkv32[:, nq + nk:].double().reshape(m, kv_heads, vdim)
         if q_gain32 is not None:
             q = q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_gain32.double()
             k = k / torch.sqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_gain32.double()
@@ -148,13 +149,19 @@ class TorchOps:
             ang = ctx.positions.double()[:, None] * freq32.double()[None, :]
             c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
 
+            first = slice(0, half) if layout == "half" else slice(0, rot_dims, 2)
+            second = slice(half, rot_dims) if layout == "half" else slice(1, rot_dims, 2)
+
             def turn(x):
-                a, b = x[..., :half].clone(), x[..., half:rot_dims].clone()
+                a, b = x[..., first].clone(), x[..., second].clone()
                 x = x.clone()
-                x[..., :half] = a * c - b * s
-                x[..., half:rot_dims] = b * c + a * s
+                x[..., first] = a * c - b * s
+                x[..., second] = b * c + a * s
                 return x
             q, k = turn(q), turn(k)
+        if unit_norm_after:
+            q = q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps)
+            k = k / torch.sqrt(k.pow(2).mean(-1, keepdim=True) + eps)
         q_out.copy_(q.reshape(m, nq).to(q_out.dtype))
         if not writes:
             return
@@ -351,21 +358,25 @@ class TorchOps:
 
     # ---- attention through a latent (latent_attention.cu) ---------------------------------------------
     @staticmethod
-    def _turn(x, positions, freq32, mag):
-        """Interleaved pairs of the last axis turned by position * freq (angles in 32-bit, as the kernels form them)."""
+    def _turn(x, positions, freq32, mag, layout="interleaved"):
+        """Pairs of the last axis (2i, 2i + 1, or with the layout "half" i, i + n/2) turned by position * freq (angles in
+        32-bit, as the kernels form them)."""
         ang = (positions.to(torch.float32)[:, None] * freq32[None, :]).double()
         c, s = ang.cos() * mag, ang.sin() * mag
         while c.dim() < x.dim():
             c, s = c.unsqueeze(1), s.unsqueeze(1)
+        n = x.shape[-1]
+        first = slice(0, n, 2) if layout == "interleaved" else slice(0, n // 2)
+        second = slice(1, n, 2) if layout == "interleaved" else slice(n // 2, n)
         out = torch.empty_like(x)
-        out[..., 0::2] = x[..., 0::2] * c - x[..., 1::2] * s
-        out[..., 1::2] = x[..., 1::2] * c + x[..., 0::2] * s
+        out[..., first] = x[..., first] * c - x[..., second] * s
+        out[..., second] = x[..., second] * c + x[..., first] * s
         return out
 
-    def latent_store(self, z32, gain32, eps, freq32, mag, ctx, block_table, page_size, pages, rank, rot):
+    def latent_store(self, z32, gain32, eps, freq32, mag, ctx, block_table, page_size, pages, rank, rot, layout="interleaved"):
         z = z32.double()
         c = z[:, :rank] / torch.sqrt(z[:, :rank].pow(2).mean(-1, keepdim=True) + eps) * gain32.double()
-        kr = self._turn(z[:, rank:], ctx.positions, freq32, mag)
+        kr = self._turn(z[:, rank:], ctx.positions, freq32, mag, layout)
         pos = ctx.positions.long()
         page = block_table[ctx.req_index.long(), pos // page_size].long()
         ok = page >= 0
@@ -374,13 +385,13 @@ class TorchOps:
     def latent_query_layout(self, dtype, rank, rot):
         return rank + rot, torch.float32
 
-    def latent_query(self, q32, w_uk, freq32, mag, positions, qa32, heads, dn, rank, rot):
+    def latent_query(self, q32, w_uk, freq32, mag, positions, qa32, heads, dn, rank, rot, layout="interleaved"):
         m = q32.shape[0]
         q = q32.double().view(m, heads, dn + rot)
         lat = torch.einsum("thd,hdc->thc", q[..., :dn], w_uk.double().view(heads, dn, rank))
-        qa32.copy_(torch.cat([lat, self._turn(q[..., dn:], positions, freq32, mag)], -1).reshape(m, -1).to(torch.float32))
+        qa32.copy_(torch.cat([lat, self._turn(q[..., dn:], positions, freq32, mag, layout)], -1).reshape(m, -1).to(torch.float32))
 
-    def latent_attention(self, qa32, lat32, ctx, block_table, page_size, pages, heads, rank, rot, scale, window):
+    def latent_attention(self, qa32, lat32, ctx, block_table, page_size, pages, heads, rank, rot, scale, window, sink32=None):
         m = qa32.shape[0]
         q = qa32.double().view(m, heads, rank + rot)
         positions, req_index = ctx.positions.tolist(), ctx.req_index.tolist()
@@ -395,13 +406,44 @@ class TorchOps:
                 continue
             rows = pages[pg, 0, idx % page_size, :].double()             # [n, rank + rot]
             s = torch.einsum("hc,nc->hn", q[t], rows) * scale
-            w = torch.softmax(s, dim=-1)
+            if sink32 is not None:      # one more column in the softmax, with nothing behind it
+                s = torch.cat([s, sink32.double()[:, None]], -1)
+            w = torch.softmax(s, dim=-1)[:, :rows.shape[0]]
             lat32[t] = (w @ rows[:, :rank]).reshape(-1).to(torch.float32)
 
-    def latent_value(self, lat32, w_uv, out, heads, dv, rank):
+    def latent_value(self, lat32, w_uv, out, heads, dv, rank, gate32=None):
         m = lat32.shape[0]
-        v = torch.einsum("thc,hjc->thj", lat32.double().view(m, heads, rank), w_uv.double().view(heads, dv, rank))
-        out.copy_(v.reshape(m, heads * dv).to(out.dtype))
+        v = torch.einsum("thc,hjc->thj", lat32.double().view(m, heads, rank), w_uv.double().view(heads, dv, rank)).reshape(m, heads * dv)
+        if gate32 is not None:
+            v = v * torch.sigmoid(gate32.double())
+        out.copy_(v.to(out.dtype))
+
+    # ---- the norm on a branch's output, and routed experts (pointwise.cu, moe.cu) -----------------------------
+    def rmsnorm_add(self, y32, gain32, eps, mult, x32, h_out=None, clear=False):
+        y = y32.double()
+        x = x32.double() + mult * y / torch.sqrt(y.pow(2).mean(-1, keepdim=True) + eps) * gain32.double()
+        x32.copy_(x.to(torch.float32))
+        if h_out is not None:
+            h_out.copy_(x32.to(h_out.dtype))
+        if clear:
+            y32.zero_()
+
+    def moe_route(self, z32, top, sel_e, sel_w):
+        order = torch.sort(z32.double(), dim=-1, descending=True, stable=True).indices[:, :top]
+        sel_e.copy_(order.to(torch.int32))
+        sel_w.copy_(torch.sigmoid(torch.gather(z32.double(), 1, order)).to(torch.float32))
+
+    def moe_experts(self, h, sel_e, sel_w, w_gate_up, w_down, out32):
+        ff = w_gate_up.shape[1] // 2
+        acc = out32.double()
+        for t in range(h.shape[0]):
+            for c in range(sel_e.shape[1]):
+                e, w = int(sel_e[t, c]), sel_w[t, c].double()
+                g = (w_gate_up[e, :ff].double() @ h[t].double()) * w
+                u = (w_gate_up[e, ff:].double() @ h[t].double()) * w
+                act = (g / (1.0 + torch.exp(-g)) * u).to(h.dtype).double()
+                acc[t] += w_down[e].double() @ act
+        out32.copy_(acc.to(torch.float32))
 
     def argmax(self, logits, out):
         out.copy_(torch.argmax(logits, dim=-1).to(out.dtype))
