@@ -529,8 +529,37 @@ def vafozen_configs(size: dict):
     return vaf, design_configs(dict(DESIGN_SIZES["1k"], **{k: size[k] for k in ("width", "heads", "head_dim", "ff_swiglu", "vocab", "layers")}))[1]
 
 
+# A Darotar stack at the same widths: attention through a latent (sink, output gate; every second such layer reads the
+# rows of the one before) and windowed attention whose values are the keys, by turns; every feed-forward is a mixture of
+# 8 experts of which a token uses 2, each half as wide as the Qwen2 decoder's feed-forward, so that a token passes through
+# as many feed-forward parameters in both models. The attention layers have the Qwen2 decoder's head counts and head size.
+DAROTAR_SIZES = {
+    "1k": {"width": 1024, "heads": 16, "head_dim": 64, "ff_swiglu": 2816, "rot": 32, "kv_rank": 128, "q_rank": 384,
+           "experts": 8, "top": 2, "window": 1024, "vocab": 32000, "layers": 8},
+    "2k": {"width": 2048, "heads": 16, "head_dim": 128, "ff_swiglu": 5632, "rot": 64, "kv_rank": 128, "q_rank": 768,
+           "experts": 8, "top": 2, "window": 1024, "vocab": 32000, "layers": 8},
+}
+
+
+def darotar_configs(size: dict):
+    w, h, d = size["width"], size["heads"], size["head_dim"]
+    ff = {"kind": "moe", "expert": {"ff": size["ff_swiglu"] // size["top"]}, "router": {"experts": size["experts"], "top": size["top"]}}
+    lat = {"heads": h, "dim": d, "rot_dim": size["rot"], "vdim": d, "q_rank": size["q_rank"], "kv_rank": size["kv_rank"],
+           "scale": (d + size["rot"]) ** -0.5, "rot": {"dims": size["rot"], "base": 10000.0}}
+    att = {"heads": h, "kv_heads": 2, "dim": d, "vdim": d, "scale": 8.0 / d, "mask": {"size": size["window"]},
+           "rot": {"dims": d, "base": 10000.0, "scaling": {"factor": 2.0}}}
+    layers = []
+    for i in range(size["layers"]):
+        if i % 2:
+            layers.append({"type": "attention", "mixer": att, "mlp": ff})
+        else:
+            layers.append({"type": "latent_attention", "mixer": dict(lat, kv_from=i - 2) if i % 4 == 2 else dict(lat), "mlp": ff})
+    dar = {"architecture": "Darotar", "vocab": size["vocab"], "width": w, "norm": {"eps": 1e-5}, "residual_mult": 0.5, "layers": layers}
+    return dar, design_configs(dict(DESIGN_SIZES["1k"], **{k: size[k] for k in ("width", "heads", "head_dim", "ff_swiglu", "vocab", "layers")}))[1]
+
+
 def run_design(args) -> dict:
-    """Prefill and decode throughput of a design (Nezalorn, Vafozen) beside the Qwen2 decoder at equal size (random
+    """Prefill and decode throughput of a design (Nezalorn, Vafozen, Darotar) beside the Qwen2 decoder at equal size (random
     weights, bfloat16, device-timed with CUDA events), and where one eager step's time goes, launch kind by launch kind."""
     import numpy as np
     import torch
@@ -542,7 +571,8 @@ def run_design(args) -> dict:
     t_pre, batch, ctx = args.prefill_tokens, args.batch, min(args.context, 2048)
     steps, warmup = min(args.steps, 64), max(3, args.warmup)
     design = args.design
-    sizes, configs = {"nezalorn": (DESIGN_SIZES, design_configs), "vafozen": (VAFOZEN_SIZES, vafozen_configs)}[design]
+    sizes, configs = {"nezalorn": (DESIGN_SIZES, design_configs), "vafozen": (VAFOZEN_SIZES, vafozen_configs),
+                      "darotar": (DAROTAR_SIZES, darotar_configs)}[design]
     out = {"impl": "ours", "design": design, "dtype": "bf16", "data": "synthetic: seeded random weights and random token ids",
            "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk["source"]},
            "config": {"prefill_tokens": t_pre, "decode_batch": batch, "decode_context": ctx, "page_size": 16}, "sizes": {}}
@@ -774,7 +804,7 @@ def main() -> int:
                     help="add a 'kernels' block: where the time of a decode step and of a prompt portion goes, kernel kind by "
                          "kind, with bytes or FLOPs and the fraction of the measured peak")
     ap.add_argument("--shape", default="0.5b", choices=sorted(SHAPES), help="layer sizes: the family's 0.5B (default), 1.5B or 7B")
-    ap.add_argument("--design", default=None, choices=["nezalorn", "vafozen"],
+    ap.add_argument("--design", default=None, choices=["nezalorn", "vafozen", "darotar"],
                     help="instead of the headline workload: prefill and decode throughput of this design beside the Qwen2 "
                          "decoder at equal size (--design-sizes, --prefill-tokens, --batch, --context up to 2048, --breakdown)")
     ap.add_argument("--design-sizes", default="", help="comma-separated names of DESIGN_SIZES (default: all)")

@@ -88,7 +88,8 @@ class Kernels:
                      "nib_head_product_nk", "nib_head_product_kn", "nib_depth_mix_norm_pair", "nib_embed_scaled", "nib_gated_norm",
                      "nib_linear_state_scan", "nib_conv_tokens", "nib_conv_tail", "nib_conv_step", "nib_token_shift", "nib_decay_map", "nib_step_sizes",
                      "nib_attention_prepare", "nib_attention_flex", "nib_attention_flex_mma", "nib_attention_flex_mma_supported",
-                     "nib_rmsnorm_add", "nib_moe_route", "nib_moe_max_tiles", "nib_moe_group", "nib_moe_gemm_simt", "nib_moe_combine"):
+                     "nib_rmsnorm_add", "nib_moe_route", "nib_moe_max_tiles", "nib_moe_group", "nib_moe_gemm_simt", "nib_moe_combine",
+                     "nib_moe_tc_supported", "nib_moe_tc_error", "nib_moe_gather_rows", "nib_moe_gemm_tc"):
             getattr(self._lib, name).restype = c_int
 
     # ---- plumbing ---------------------------------------------------------------------------
@@ -540,6 +541,7 @@ class Kernels:
             ("tensor-core GEMM (gemm_tcgen05.cu)", self.gemm_tc_error(), _GEMM_TC_ROLES),
             ("tcgen05 prefill attention (attention_tcgen05.cu)", self.attention_tc_error(), _ATTN_TC_ROLES),
             ("TMA decode attention (attention_decode_tma.cu)", self.attention_decode_tma_error(), _DECODE_TMA_ROLES),
+            ("routed experts on the tensor cores (moe_tcgen05.cu)", self._lib.nib_moe_tc_error(), _GEMM_TC_ROLES),
         ])
 
     def decode_splits(self, n_tokens: int, kv_heads: int, max_ctx: int, window: int, tma: bool = False,
@@ -708,21 +710,36 @@ class Kernels:
         if m == 0:
             return
         n, dev, dt = m * top, h.device, c_int(_DT[h.dtype])
-        tile_rows = 64
+        # bfloat16 in widths of 8: the tensor-core products over row tiles of 128 (of 32 while an expert gets few rows: a
+        # decode step); everything else (32-bit, odd widths): the CUDA-core product over row tiles of 64
+        tc = h.dtype == torch.bfloat16 and not self.options.force_simt_gemm and self._lib.nib_moe_tc_supported(
+            _ptr(h), c_int(h.stride(0)), _ptr(w_gate_up), _ptr(w_down), c_int(experts), c_int(hidden), c_int(ff)) == 1
+        tile_rows = (32 if n <= 32 * experts else 128) if tc else 64
         max_tiles = self._lib.nib_moe_max_tiles(c_int(n), c_int(experts), c_int(tile_rows))
         idx = torch.empty(2 * n + 3 * max_tiles + 1, dtype=torch.int32, device=dev)
         row_of, src_of, tiles, n_tiles = idx[:n], idx[n:2 * n], idx[2 * n:2 * n + 3 * max_tiles], idx[2 * n + 3 * max_tiles:]
         self._check(self._lib.nib_moe_group(_ptr(sel_e), c_int(n), c_int(experts), c_int(tile_rows), _ptr(row_of), _ptr(src_of), _ptr(tiles),
                                             _ptr(n_tiles), c_int(max_tiles), self._stream()), "moe_group")
         act = torch.empty((n, ff), dtype=h.dtype, device=dev)
-        self._check(self._lib.nib_moe_gemm_simt(c_int(1), _ptr(h), c_int(h.stride(0)), _ptr(w_gate_up), _ptr(act), c_int(ff), _ptr(tiles), _ptr(n_tiles),
-                                                c_int(max_tiles), _ptr(src_of), _ptr(sel_w), c_int(top), c_int(ff), c_int(hidden), c_int(0), dt,
-                                                self._stream()), "experts: gate, up, activation")
         scatter = top == 1      # one choice per token: its result goes straight into the token's row
         y = out32 if scatter else torch.empty((n, hidden), dtype=torch.float32, device=dev)
-        self._check(self._lib.nib_moe_gemm_simt(c_int(0), _ptr(act), c_int(ff), _ptr(w_down), _ptr(y), c_int(y.stride(0)), _ptr(tiles), _ptr(n_tiles),
-                                                c_int(max_tiles), _ptr(src_of), _ptr(sel_w), c_int(top), c_int(hidden), c_int(ff), c_int(1 if scatter else 0),
-                                                dt, self._stream()), "experts: down")
+        if tc:
+            rows = torch.empty((n, hidden), dtype=h.dtype, device=dev)
+            self._check(self._lib.nib_moe_gather_rows(_ptr(h), c_int(h.stride(0)), _ptr(rows), c_int(hidden), _ptr(src_of), c_int(n), c_int(hidden),
+                                                      c_int(top), self._stream()), "experts: rows in the experts' order")
+            self._check(self._lib.nib_moe_gemm_tc(c_int(1), _ptr(rows), c_int(hidden), c_int(n), _ptr(w_gate_up), c_int(experts), _ptr(act), c_int(ff),
+                                                  _ptr(tiles), _ptr(n_tiles), c_int(max_tiles), _ptr(src_of), _ptr(sel_w), c_int(top), c_int(ff),
+                                                  c_int(hidden), c_int(0), c_int(tile_rows), self._stream()), "experts: gate, up, activation (tensor cores)")
+            self._check(self._lib.nib_moe_gemm_tc(c_int(0), _ptr(act), c_int(ff), c_int(n), _ptr(w_down), c_int(experts), _ptr(y), c_int(y.stride(0)),
+                                                  _ptr(tiles), _ptr(n_tiles), c_int(max_tiles), _ptr(src_of), _ptr(sel_w), c_int(top), c_int(hidden),
+                                                  c_int(ff), c_int(1 if scatter else 0), c_int(tile_rows), self._stream()), "experts: down (tensor cores)")
+        else:
+            self._check(self._lib.nib_moe_gemm_simt(c_int(1), _ptr(h), c_int(h.stride(0)), _ptr(w_gate_up), _ptr(act), c_int(ff), _ptr(tiles), _ptr(n_tiles),
+                                                    c_int(max_tiles), _ptr(src_of), _ptr(sel_w), c_int(top), c_int(ff), c_int(hidden), c_int(0), dt,
+                                                    self._stream()), "experts: gate, up, activation")
+            self._check(self._lib.nib_moe_gemm_simt(c_int(0), _ptr(act), c_int(ff), _ptr(w_down), _ptr(y), c_int(y.stride(0)), _ptr(tiles), _ptr(n_tiles),
+                                                    c_int(max_tiles), _ptr(src_of), _ptr(sel_w), c_int(top), c_int(hidden), c_int(ff), c_int(1 if scatter else 0),
+                                                    dt, self._stream()), "experts: down")
         if not scatter:
             self._check(self._lib.nib_moe_combine(_ptr(y), _ptr(row_of), _ptr(out32), c_int(m), c_int(hidden), c_int(top), self._stream()),
                         "experts: sum of a token's choices")

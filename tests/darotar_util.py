@@ -91,6 +91,27 @@ def write_model(folder, cfg, seed, weights=None):
     return folder
 
 
+def pin_routing(cfg, classes=8):
+    """A change of the random tensors after which the routing is the same in every precision: the first ``classes``
+    channels of the stream hold a one-hot class of the token (token id modulo ``classes``), no branch ever adds to them
+    (the gains of every norm are zero there), and the routers read nothing else. Every router logit is then one product
+    of two numbers that bfloat16 holds, equal in 16, 32 and 64 bits, so a comparison of bfloat16 logits with the plain
+    implementation cannot rest on a close call between two experts (in 32-bit the tests keep the random routers).
+    The experts still read the whole stream, each token scaled by its score."""
+    def change(t):
+        emb = t["embed"]
+        emb[:, :classes] = 0
+        emb[torch.arange(emb.shape[0]), torch.arange(emb.shape[0]) % classes] = 2.0
+        for i, layer in enumerate(cfg["layers"]):
+            t[f"l{i}.norm1"][:classes] = 0
+            if layer.get("mlp") is not None:
+                t[f"l{i}.norm2"][:classes] = 0
+                r = t[f"l{i}.mlp.router"]
+                r[:, classes:] = 0
+                r[:, :classes] = (torch.randn(r.shape[0], classes, generator=torch.Generator().manual_seed(100 + i)) * 0.6).to(r.dtype)
+    return change
+
+
 def read_model(folder):
     from nanoinfer_b200.weights.safetensors_io import SafetensorsFile
     with open(os.path.join(folder, "config.json")) as f:
@@ -99,11 +120,30 @@ def read_model(folder):
     return cfg, {n: sf.tensor(n) for n in sf.names()}
 
 
-def plain_logits(folder, ids):
-    """Float64 logits [len(ids), vocab] of the plain implementation."""
+def plain_logits(folder, ids, stored_as=None):
+    """Float64 logits [len(ids), vocab] of the plain implementation; with ``stored_as`` every tensor that an engine keeps
+    between two operations is rounded to that type on the way."""
     import plain_darotar as plain
     cfg, w = read_model(folder)
-    return plain.logits(cfg, w, list(ids))
+    if stored_as is None:
+        return plain.logits(cfg, w, list(ids))
+    with plain.stored_as(stored_as):
+        return plain.logits(cfg, w, list(ids))
+
+
+def assert_within_rounding(got, ref, rounded, what="", factor=3.0):
+    """``got`` (an engine in bfloat16) against ``ref`` (the plain implementation in float64), judged by what rounding alone
+    does to this model: ``rounded`` is the plain implementation with its stored tensors rounded to bfloat16. Root mean
+    square and largest error may be ``factor`` times those of ``rounded``; an error that a wrong key, window or state
+    makes is of the order of the logits themselves."""
+    got, ref, rounded = got.detach().double().cpu(), ref.double(), rounded.double()
+    assert got.shape == ref.shape, (what, got.shape, ref.shape)
+    assert not torch.isnan(got).any() and not torch.isinf(got).any(), f"{what}: NaN or inf in the result"
+    err, noise = (got - ref).abs(), (rounded - ref).abs()
+    e_rms, n_rms = err.pow(2).mean().sqrt().item(), noise.pow(2).mean().sqrt().item()
+    assert n_rms < 0.05 * ref.pow(2).mean().sqrt().item(), f"{what}: rounding alone moves this model's logits too far to judge by"
+    assert e_rms <= factor * n_rms, f"{what}: rms err {e_rms:.3e} > {factor} x {n_rms:.3e}"
+    assert err.max().item() <= factor * noise.max().item(), f"{what}: max err {err.max().item():.3e} > {factor} x {noise.max().item():.3e}"
 
 
 def tokens(n, vocab, seed):

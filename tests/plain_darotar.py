@@ -10,6 +10,29 @@ import torch
 
 F = torch.float64
 
+# With a storage type set (``with stored_as(torch.bfloat16):``) every tensor that an engine would keep in that type between
+# two operations (what the sublayers read, projections, cached rows, activations) is rounded to it and taken on in
+# float64. The difference to the unrounded result is what rounding alone does to this model's logits: the tests judge
+# an engine's bfloat16 results by a multiple of it.
+_STORED = None
+
+
+class stored_as:
+    def __init__(self, dtype):
+        self.dtype = dtype
+
+    def __enter__(self):
+        global _STORED
+        self.before, _STORED = _STORED, self.dtype
+
+    def __exit__(self, *exc):
+        global _STORED
+        _STORED = self.before
+
+
+def kept(x):
+    return x if _STORED is None else x.to(_STORED).to(F)
+
 
 def rms_unit(x, eps):
     return x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps)
@@ -81,16 +104,16 @@ def attention_mixer(m, w, p, h, eps):
     heads, groups, dim = int(m["heads"]), int(m["kv_heads"]), int(m["dim"])
     q = (h @ w[p + ".q"].t()).view(t_len, heads, dim)
     k = (h @ w[p + ".k"].t()).view(t_len, groups, dim)
-    v = k.clone()
+    v = kept(k)
     q, k = rotate_interleaved(q, m["rot"]), rotate_interleaved(k, m["rot"])
-    q, k = rms_unit(q, eps), rms_unit(k, eps)
+    q, k = kept(rms_unit(q, eps)), kept(rms_unit(k, eps))
     mask = visible(t_len, m["mask"]["size"] if m.get("mask") else None)
     rep = heads // groups
     out = torch.zeros(t_len, heads, dim, dtype=F)
     for n in range(heads):
         s = (q[:, n] @ k[:, n // rep].t()) * float(m["scale"])
         out[:, n] = softmax_rows(s, mask) @ v[:, n // rep]
-    return out.reshape(t_len, -1) @ w[p + ".o"].t()
+    return kept(out).reshape(t_len, -1) @ w[p + ".o"].t()
 
 
 def latent_rows(m, w, p, h, eps):
@@ -99,7 +122,7 @@ def latent_rows(m, w, p, h, eps):
     z = h @ w[p + ".dkv"].t()
     c = norm(z[:, :rank], w[p + ".dkv.norm"], eps)
     kr = rotate_half(z[:, None, rank:], m["rot"])[:, 0]
-    return c, kr
+    return kept(c), kept(kr)
 
 
 def latent_mixer(m, w, p, h, eps, rows):
@@ -108,9 +131,9 @@ def latent_mixer(m, w, p, h, eps, rows):
     t_len = h.shape[0]
     heads, dim, rdim, vdim = int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"])
     c, kr = rows
-    cq = norm(h @ w[p + ".dq"].t(), w[p + ".dq.norm"], eps)
+    cq = kept(norm(h @ w[p + ".dq"].t(), w[p + ".dq.norm"], eps))
     q = (cq @ w[p + ".uq"].t()).view(t_len, heads, dim + rdim)
-    q_plain, q_rot = q[..., :dim], rotate_half(q[..., dim:], m["rot"])
+    q_plain, q_rot = kept(q[..., :dim]), kept(rotate_half(q[..., dim:], m["rot"]))
     k_plain = (c @ w[p + ".uk"].t()).view(t_len, heads, dim)
     v = (c @ w[p + ".uv"].t()).view(t_len, heads, vdim)
     mask = visible(t_len, m["mask"]["size"] if m.get("mask") else None)
@@ -119,7 +142,7 @@ def latent_mixer(m, w, p, h, eps, rows):
         s = (q_plain[:, n] @ k_plain[:, n].t() + q_rot[:, n] @ kr.t()) * float(m["scale"])
         out[:, n] = softmax_rows(s, mask, sink=w[p + ".sink"][n]) @ v[:, n]
     gate = torch.sigmoid(h @ w[p + ".g"].t())
-    return (out.reshape(t_len, -1) * gate) @ w[p + ".o"].t()
+    return kept(out.reshape(t_len, -1) * gate) @ w[p + ".o"].t()
 
 
 def routed_experts(mlp, w, p, h):
@@ -133,7 +156,7 @@ def routed_experts(mlp, w, p, h):
             x = s[t, e] * h[t]
             g = x @ w[f"{p}.e{e}.gate"].t()
             u = x @ w[f"{p}.e{e}.up"].t()
-            out[t] += (g * torch.sigmoid(g) * u) @ w[f"{p}.e{e}.down"].t()
+            out[t] += kept(g * torch.sigmoid(g) * u) @ w[f"{p}.e{e}.down"].t()
     assert n_exp >= top
     return out
 
@@ -146,19 +169,20 @@ def forward(cfg, w, ids):
     cached = {}
     for i, layer in enumerate(cfg["layers"]):
         m, p = layer["mixer"], f"l{i}.mix"
+        h = kept(x)         # the sublayers read the stream itself (an engine: in its storage type)
         if layer["type"] == "attention":
-            y = attention_mixer(m, w, p, x, eps)
+            y = attention_mixer(m, w, p, h, eps)
         else:
             src = m.get("kv_from")
             if src is None:
-                cached[i] = latent_rows(m, w, p, x, eps)
+                cached[i] = latent_rows(m, w, p, h, eps)
                 src = i
-            y = latent_mixer(m, w, p, x, eps, cached[src])
+            y = latent_mixer(m, w, p, h, eps, cached[src])
         x = x + mult * norm(y, w[f"l{i}.norm1"], eps)
         if layer.get("mlp") is not None:
-            x = x + mult * norm(routed_experts(layer["mlp"], w, f"l{i}.mlp", x), w[f"l{i}.norm2"], eps)
+            x = x + mult * norm(routed_experts(layer["mlp"], w, f"l{i}.mlp", kept(x)), w[f"l{i}.norm2"], eps)
         streams.append(x)
-    return norm(x, w["final.norm"], eps) @ w["head"].t(), streams
+    return kept(norm(x, w["final.norm"], eps)) @ w["head"].t(), streams
 
 
 def logits(cfg, w, ids):
