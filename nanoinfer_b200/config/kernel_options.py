@@ -27,6 +27,7 @@ class KernelOptions:
     smallm_ksplit: int = 0                  # K split among the warps of a CTA in the small-M product (0 = chosen; 1, 8)
     smallm_cross: int = 0                   # CTAs that split K further in the small-M product (0 = chosen)
     fuse_qkv: bool = True                   # up to 16 tokens: bias, rotation and the page write are the q/k/v product's epilogue
+    no_moe_step: bool = False               # routed experts: router, choice and grouping as separate launches for short steps too
 
     def __post_init__(self):
         if self.gemm_route not in _ROUTES:

@@ -6,6 +6,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
+from types import SimpleNamespace
 from typing import Optional
 
 import torch
@@ -89,7 +90,7 @@ class Kernels:
                      "nib_linear_state_scan", "nib_conv_tokens", "nib_conv_tail", "nib_conv_step", "nib_token_shift", "nib_decay_map", "nib_step_sizes",
                      "nib_attention_prepare", "nib_attention_flex", "nib_attention_flex_mma", "nib_attention_flex_mma_supported",
                      "nib_rmsnorm_add", "nib_moe_route", "nib_moe_max_tiles", "nib_moe_group", "nib_moe_gemm_simt", "nib_moe_combine",
-                     "nib_moe_tc_supported", "nib_moe_tc_error", "nib_moe_gather_rows", "nib_moe_gemm_tc"):
+                     "nib_moe_tc_supported", "nib_moe_tc_error", "nib_moe_gather_rows", "nib_moe_gemm_tc", "nib_moe_step", "nib_moe_step_supported"):
             getattr(self._lib, name).restype = c_int
 
     # ---- plumbing ---------------------------------------------------------------------------
@@ -695,10 +696,47 @@ class Kernels:
         self._check(self._lib.nib_moe_route(_ptr(z32), c_int(z32.stride(0)), _ptr(sel_e), _ptr(sel_w), c_int(m), c_int(experts), c_int(top),
                                             self._stream()), "moe_route")
 
-    def moe_experts(self, h, sel_e, sel_w, w_gate_up, w_down, out32):
+    def _moe_tc(self, h, w_gate_up, w_down) -> bool:
+        """bfloat16 in widths of 8 takes the tensor-core products; everything else (32-bit, odd widths) the CUDA cores."""
+        experts, ff2, hidden = w_gate_up.shape
+        return h.dtype == torch.bfloat16 and not self.options.force_simt_gemm and self._lib.nib_moe_tc_supported(
+            _ptr(h), c_int(h.stride(0)), _ptr(w_gate_up), _ptr(w_down), c_int(experts), c_int(hidden), c_int(ff2 // 2)) == 1
+
+    def _moe_tables(self, n, experts, tc, dev):
+        """Row tiles of 128 for the tensor cores (of 32 while an expert gets few rows: a decode step), of 64 for the CUDA
+        cores; the index arrays of ``n`` entries: row_of, src_of, the tile table and its length."""
+        tile_rows = (32 if n <= 32 * experts else 128) if tc else 64
+        max_tiles = self._lib.nib_moe_max_tiles(c_int(n), c_int(experts), c_int(tile_rows))
+        idx = torch.empty(2 * n + 3 * max_tiles + 1, dtype=torch.int32, device=dev)
+        return SimpleNamespace(tile_rows=tile_rows, max_tiles=max_tiles, row_of=idx[:n], src_of=idx[n:2 * n],
+                               tiles=idx[2 * n:2 * n + 3 * max_tiles], n_tiles=idx[2 * n + 3 * max_tiles:], rows=None)
+
+    def moe_step(self, h, w_router, top, w_gate_up, w_down, sel_e, sel_w):
+        """A step of few tokens: router logits (32-bit sums over the stored ``h``), the choice, the grouping and the rows
+        in the experts' order in ONE launch. Fills sel_e and sel_w like ``moe_route`` and returns what ``moe_experts``
+        takes as ``plan``; None when the step is too large for one block (the caller then takes the separate steps)."""
+        _need(h, None, "moe_step h"); _need(w_router, h.dtype, "moe_step router")
+        m, hidden = h.shape
+        experts = w_router.shape[0]
+        if m == 0 or self.options.no_moe_step or self._lib.nib_moe_step_supported(c_int(m), c_int(hidden), c_int(experts), c_int(top)) != 1:
+            return None
+        tc = self._moe_tc(h, w_gate_up, w_down)
+        plan = self._moe_tables(m * top, experts, tc, h.device)
+        if tc:
+            plan.rows = torch.empty((m * top, hidden), dtype=h.dtype, device=h.device)
+        self._check(self._lib.nib_moe_step(_ptr(h), c_int(h.stride(0)), _ptr(w_router), c_int(m), c_int(hidden), c_int(experts), c_int(top),
+                                           _ptr(sel_e), _ptr(sel_w), c_int(plan.tile_rows), _ptr(plan.row_of), _ptr(plan.src_of), _ptr(plan.tiles),
+                                           _ptr(plan.n_tiles), c_int(plan.max_tiles), _ptr(plan.rows), c_int(_DT[h.dtype]), self._stream()),
+                    "experts: router, choice and grouping of a short step")
+        return plan
+
+    def moe_experts(self, h, sel_e, sel_w, w_gate_up, w_down, out32, plan=None):
         """out32[t] += sum over the token's choices c of W_down,e (silu(W_gate,e x) * (W_up,e x)) with e = sel_e[t, c] and
         x = sel_w[t, c] * h[t]: the weight stands on the expert's input. w_gate_up [experts, 2 ff, hidden] (gate rows, then up
-        rows), w_down [experts, hidden, ff]. The choices are summed in ascending order."""
+        rows), w_down [experts, hidden, ff]. ``plan``: what ``moe_step`` returned for these choices.
+
+        On the CUDA cores a token's choices are summed in ascending order; on the tensor cores they are added into the
+        token's row by reductions in memory, in no fixed order."""
         _need(h, None, "moe_experts h"); _need(w_gate_up, h.dtype, "moe_experts w_gate_up"); _need(w_down, h.dtype, "moe_experts w_down")
         _need(sel_e, torch.int32, "moe_experts experts"); _need(sel_w, torch.float32, "moe_experts weights"); _need(out32, torch.float32, "moe_experts out")
         m, hidden = h.shape
@@ -710,38 +748,35 @@ class Kernels:
         if m == 0:
             return
         n, dev, dt = m * top, h.device, c_int(_DT[h.dtype])
-        # bfloat16 in widths of 8: the tensor-core products over row tiles of 128 (of 32 while an expert gets few rows: a
-        # decode step); everything else (32-bit, odd widths): the CUDA-core product over row tiles of 64
-        tc = h.dtype == torch.bfloat16 and not self.options.force_simt_gemm and self._lib.nib_moe_tc_supported(
-            _ptr(h), c_int(h.stride(0)), _ptr(w_gate_up), _ptr(w_down), c_int(experts), c_int(hidden), c_int(ff)) == 1
-        tile_rows = (32 if n <= 32 * experts else 128) if tc else 64
-        max_tiles = self._lib.nib_moe_max_tiles(c_int(n), c_int(experts), c_int(tile_rows))
-        idx = torch.empty(2 * n + 3 * max_tiles + 1, dtype=torch.int32, device=dev)
-        row_of, src_of, tiles, n_tiles = idx[:n], idx[n:2 * n], idx[2 * n:2 * n + 3 * max_tiles], idx[2 * n + 3 * max_tiles:]
-        self._check(self._lib.nib_moe_group(_ptr(sel_e), c_int(n), c_int(experts), c_int(tile_rows), _ptr(row_of), _ptr(src_of), _ptr(tiles),
-                                            _ptr(n_tiles), c_int(max_tiles), self._stream()), "moe_group")
+        tc = self._moe_tc(h, w_gate_up, w_down)
+        p = plan
+        if p is None:
+            p = self._moe_tables(n, experts, tc, dev)
+            self._check(self._lib.nib_moe_group(_ptr(sel_e), c_int(n), c_int(experts), c_int(p.tile_rows), _ptr(p.row_of), _ptr(p.src_of), _ptr(p.tiles),
+                                                _ptr(p.n_tiles), c_int(p.max_tiles), self._stream()), "moe_group")
         act = torch.empty((n, ff), dtype=h.dtype, device=dev)
+        if tc:
+            if p.rows is None:
+                p.rows = torch.empty((n, hidden), dtype=h.dtype, device=dev)
+                self._check(self._lib.nib_moe_gather_rows(_ptr(h), c_int(h.stride(0)), _ptr(p.rows), c_int(hidden), _ptr(p.src_of), c_int(n), c_int(hidden),
+                                                          c_int(top), self._stream()), "experts: rows in the experts' order")
+            self._check(self._lib.nib_moe_gemm_tc(c_int(1), _ptr(p.rows), c_int(hidden), c_int(n), _ptr(w_gate_up), c_int(experts), _ptr(act), c_int(ff),
+                                                  _ptr(p.tiles), _ptr(p.n_tiles), c_int(p.max_tiles), _ptr(p.src_of), _ptr(sel_w), c_int(top), c_int(ff),
+                                                  c_int(hidden), c_int(0), c_int(p.tile_rows), self._stream()), "experts: gate, up, activation (tensor cores)")
+            self._check(self._lib.nib_moe_gemm_tc(c_int(0), _ptr(act), c_int(ff), c_int(n), _ptr(w_down), c_int(experts), _ptr(out32), c_int(out32.stride(0)),
+                                                  _ptr(p.tiles), _ptr(p.n_tiles), c_int(p.max_tiles), _ptr(p.src_of), _ptr(sel_w), c_int(top), c_int(hidden),
+                                                  c_int(ff), c_int(1 if top == 1 else 2), c_int(p.tile_rows), self._stream()), "experts: down (tensor cores)")
+            return
         scatter = top == 1      # one choice per token: its result goes straight into the token's row
         y = out32 if scatter else torch.empty((n, hidden), dtype=torch.float32, device=dev)
-        if tc:
-            rows = torch.empty((n, hidden), dtype=h.dtype, device=dev)
-            self._check(self._lib.nib_moe_gather_rows(_ptr(h), c_int(h.stride(0)), _ptr(rows), c_int(hidden), _ptr(src_of), c_int(n), c_int(hidden),
-                                                      c_int(top), self._stream()), "experts: rows in the experts' order")
-            self._check(self._lib.nib_moe_gemm_tc(c_int(1), _ptr(rows), c_int(hidden), c_int(n), _ptr(w_gate_up), c_int(experts), _ptr(act), c_int(ff),
-                                                  _ptr(tiles), _ptr(n_tiles), c_int(max_tiles), _ptr(src_of), _ptr(sel_w), c_int(top), c_int(ff),
-                                                  c_int(hidden), c_int(0), c_int(tile_rows), self._stream()), "experts: gate, up, activation (tensor cores)")
-            self._check(self._lib.nib_moe_gemm_tc(c_int(0), _ptr(act), c_int(ff), c_int(n), _ptr(w_down), c_int(experts), _ptr(y), c_int(y.stride(0)),
-                                                  _ptr(tiles), _ptr(n_tiles), c_int(max_tiles), _ptr(src_of), _ptr(sel_w), c_int(top), c_int(hidden),
-                                                  c_int(ff), c_int(1 if scatter else 0), c_int(tile_rows), self._stream()), "experts: down (tensor cores)")
-        else:
-            self._check(self._lib.nib_moe_gemm_simt(c_int(1), _ptr(h), c_int(h.stride(0)), _ptr(w_gate_up), _ptr(act), c_int(ff), _ptr(tiles), _ptr(n_tiles),
-                                                    c_int(max_tiles), _ptr(src_of), _ptr(sel_w), c_int(top), c_int(ff), c_int(hidden), c_int(0), dt,
-                                                    self._stream()), "experts: gate, up, activation")
-            self._check(self._lib.nib_moe_gemm_simt(c_int(0), _ptr(act), c_int(ff), _ptr(w_down), _ptr(y), c_int(y.stride(0)), _ptr(tiles), _ptr(n_tiles),
-                                                    c_int(max_tiles), _ptr(src_of), _ptr(sel_w), c_int(top), c_int(hidden), c_int(ff), c_int(1 if scatter else 0),
-                                                    dt, self._stream()), "experts: down")
+        self._check(self._lib.nib_moe_gemm_simt(c_int(1), _ptr(h), c_int(h.stride(0)), _ptr(w_gate_up), _ptr(act), c_int(ff), _ptr(p.tiles), _ptr(p.n_tiles),
+                                                c_int(p.max_tiles), _ptr(p.src_of), _ptr(sel_w), c_int(top), c_int(ff), c_int(hidden), c_int(0), dt,
+                                                self._stream()), "experts: gate, up, activation")
+        self._check(self._lib.nib_moe_gemm_simt(c_int(0), _ptr(act), c_int(ff), _ptr(w_down), _ptr(y), c_int(y.stride(0)), _ptr(p.tiles), _ptr(p.n_tiles),
+                                                c_int(p.max_tiles), _ptr(p.src_of), _ptr(sel_w), c_int(top), c_int(hidden), c_int(ff), c_int(1 if scatter else 0),
+                                                dt, self._stream()), "experts: down")
         if not scatter:
-            self._check(self._lib.nib_moe_combine(_ptr(y), _ptr(row_of), _ptr(out32), c_int(m), c_int(hidden), c_int(top), self._stream()),
+            self._check(self._lib.nib_moe_combine(_ptr(y), _ptr(p.row_of), _ptr(out32), c_int(m), c_int(hidden), c_int(top), self._stream()),
                         "experts: sum of a token's choices")
 
     # ---- gate, norm in groups, skip (pointwise.cu) ---------------------------------------------------------

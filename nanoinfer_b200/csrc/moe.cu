@@ -17,13 +17,8 @@
 
 constexpr int MOE_MAX_EXPERTS = 1024;
 
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ z, int ldz, int* __restrict__ sel_e, float* __restrict__ sel_w, int tokens, int experts, int top) {
-    pdl_launch_dependents();
-    pdl_wait();      // everything this kernel reads may come from the kernel before
-    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (t >= tokens) return;
-    const float* zr = z + (size_t)t * ldz;
+// One warp chooses for one token: the `top` largest of zr[0..experts) (the first of equal ones) and their sigmoids.
+__device__ __forceinline__ void route_token(const float* zr, int experts, int top, int lane, int* sel_e, float* sel_w) {
     unsigned taken = 0;     // bit j: this lane's expert lane + 32 j is chosen already
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
@@ -43,19 +38,25 @@ moe_route_kernel(const float* __restrict__ z, int ldz, int* __restrict__ sel_e, 
         if (bi == INT_MAX) bi = 0;
         if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
         if (lane == 0) {
-            sel_e[(size_t)t * top + k] = bi;
-            sel_w[(size_t)t * top + k] = 1.0f / (1.0f + expf(-best));
+            sel_e[k] = bi;
+            sel_w[k] = 1.0f / (1.0f + expf(-best));
         }
     }
 }
 
-// tiles: [max_tiles, 3] = (expert, first row, rows); n_tiles[0] = how many are in use.
-__global__ void __launch_bounds__(1024)
-moe_group_kernel(const int* __restrict__ sel_e, int n, int experts, int tile_rows, int* __restrict__ row_of, int* __restrict__ src_of,
-                 int* __restrict__ tiles, int* __restrict__ n_tiles, int max_tiles) {
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ z, int ldz, int* __restrict__ sel_e, float* __restrict__ sel_w, int tokens, int experts, int top) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
-    __shared__ int cnt[MOE_MAX_EXPERTS], off[MOE_MAX_EXPERTS], toff[MOE_MAX_EXPERTS], cur[MOE_MAX_EXPERTS];
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= tokens) return;
+    route_token(z + (size_t)t * ldz, experts, top, lane, sel_e + (size_t)t * top, sel_w + (size_t)t * top);
+}
+
+// The (token, choice) entries ordered by expert, by one block of any size. tiles: [max_tiles, 3] = (expert, first row,
+// rows); n_tiles[0] = how many are in use. cnt, off, toff, cur: shared arrays of MOE_MAX_EXPERTS ints.
+__device__ __forceinline__ void group_entries(const int* sel_e, int n, int experts, int tile_rows, int* row_of, int* src_of, int* tiles,
+                                              int* n_tiles, int max_tiles, int* cnt, int* off, int* toff, int* cur) {
     const int tid = threadIdx.x, lane = tid & 31;
     for (int e = tid; e < experts; e += blockDim.x) { cnt[e] = 0; cur[e] = 0; }
     __syncthreads();
@@ -90,11 +91,59 @@ moe_group_kernel(const int* __restrict__ sel_e, int n, int experts, int tile_row
             }
         }
     }
+    // a token's entries keep their order within an expert's rows only by chance: nothing reads that order
     for (int i = tid; i < n; i += blockDim.x) {
         const int e = sel_e[i];
         const int pos = off[e] + atomicAdd(&cur[e], 1);
         row_of[i] = pos;
         src_of[pos] = i;
+    }
+}
+
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int* __restrict__ sel_e, int n, int experts, int tile_rows, int* __restrict__ row_of, int* __restrict__ src_of,
+                 int* __restrict__ tiles, int* __restrict__ n_tiles, int max_tiles) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
+    __shared__ int cnt[MOE_MAX_EXPERTS], off[MOE_MAX_EXPERTS], toff[MOE_MAX_EXPERTS], cur[MOE_MAX_EXPERTS];
+    group_entries(sel_e, n, experts, tile_rows, row_of, src_of, tiles, n_tiles, max_tiles, cnt, off, toff, cur);
+}
+
+// A step of few tokens in ONE launch of one block: router logits z = W_router h (32-bit sums over the stored h), the
+// choice, the grouping, and with `rows` the tokens' rows copied into the grouped order (what the tensor-core products read).
+constexpr int MOE_STEP_MAX_Z = 2048;     // tokens * experts
+
+template <typename T>
+__global__ void __launch_bounds__(1024)
+moe_step_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ w_router, int tokens, int hidden, int experts, int top,
+                int* __restrict__ sel_e, float* __restrict__ sel_w, int tile_rows, int* __restrict__ row_of, int* __restrict__ src_of,
+                int* __restrict__ tiles, int* __restrict__ n_tiles, int max_tiles, T* __restrict__ rows) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
+    __shared__ int cnt[MOE_MAX_EXPERTS], off[MOE_MAX_EXPERTS], toff[MOE_MAX_EXPERTS], cur[MOE_MAX_EXPERTS];
+    __shared__ float z[MOE_STEP_MAX_Z];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
+    for (int p = warp; p < tokens * experts; p += warps) {      // a warp per (token, expert): ascending k within a lane
+        const int t = p / experts, e = p - t * experts;
+        const T* hr = h + (size_t)t * ldh;
+        const T* wr = w_router + (size_t)e * hidden;
+        float acc = 0.f;
+        for (int k = lane; k < hidden; k += 32) acc = fmaf(Elem<T>::load(hr + k), Elem<T>::load(wr + k), acc);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) z[p] = acc;
+    }
+    __syncthreads();
+    for (int t = warp; t < tokens; t += warps)
+        route_token(z + t * experts, experts, top, lane, sel_e + (size_t)t * top, sel_w + (size_t)t * top);
+    __syncthreads();        // the block's own writes to sel_e are visible to all of its threads
+    const int n = tokens * top;
+    group_entries(sel_e, n, experts, tile_rows, row_of, src_of, tiles, n_tiles, max_tiles, cnt, off, toff, cur);
+    if (rows == nullptr) return;
+    __syncthreads();
+    for (int i = tid; i < n * hidden; i += blockDim.x) {
+        const int r = i / hidden, c = i - r * hidden;
+        rows[(size_t)r * hidden + c] = h[(size_t)(src_of[r] / top) * ldh + c];
     }
 }
 
@@ -239,6 +288,30 @@ NIB_API int nib_moe_group(const int* sel_e, int entries, int experts, int tile_r
                 "moe_group: bad sizes");
     if (entries == 0) return 0;
     NIB_CUDA(launch_pdl(moe_group_kernel, dim3(1), dim3(1024), (size_t)0, stream, sel_e, entries, experts, tile_rows, row_of, src_of, tiles, n_tiles, max_tiles));
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+// 1 if a step of these sizes takes the one-launch form.
+NIB_API int nib_moe_step_supported(int tokens, int hidden, int experts, int top) {
+    return tokens > 0 && experts > 0 && experts <= MOE_MAX_EXPERTS && top > 0 && top <= experts && (long long)tokens * experts <= MOE_STEP_MAX_Z
+        && (long long)tokens * experts * hidden <= (1LL << 21) && (long long)tokens * top * hidden <= (1LL << 20);
+}
+
+// Router, choice, grouping and (rows != null) the gathered rows of a step of few tokens. h [tokens, hidden] and w_router
+// [experts, hidden] in the storage type; the other arguments as for moe_route and moe_group.
+NIB_API int nib_moe_step(const void* h, int ldh, const void* w_router, int tokens, int hidden, int experts, int top, int* sel_e, float* sel_w,
+                         int tile_rows, int* row_of, int* src_of, int* tiles, int* n_tiles, int max_tiles, void* rows, int dtype, cudaStream_t stream) {
+    NIB_REQUIRE(nib_moe_step_supported(tokens, hidden, experts, top) == 1 && ldh >= hidden && tile_rows > 0
+                && max_tiles >= nib_moe_max_tiles(tokens * top, experts, tile_rows), "moe_step: bad sizes");
+    NIB_REQUIRE(dtype == NIB_F32 || dtype == NIB_BF16, "moe_step: unknown dtype %d", dtype);
+    if (dtype == NIB_F32)
+        NIB_CUDA(launch_pdl(moe_step_kernel<float>, dim3(1), dim3(1024), (size_t)0, stream, (const float*)h, ldh, (const float*)w_router, tokens, hidden,
+                            experts, top, sel_e, sel_w, tile_rows, row_of, src_of, tiles, n_tiles, max_tiles, (float*)rows));
+    else
+        NIB_CUDA(launch_pdl(moe_step_kernel<__nv_bfloat16>, dim3(1), dim3(1024), (size_t)0, stream, (const __nv_bfloat16*)h, ldh,
+                            (const __nv_bfloat16*)w_router, tokens, hidden, experts, top, sel_e, sel_w, tile_rows, row_of, src_of, tiles, n_tiles,
+                            max_tiles, (__nv_bfloat16*)rows));
     NIB_LAUNCH_CHECK();
     return 0;
 }

@@ -4,7 +4,9 @@
 //
 //   gate/up:  act[row] = silu(w g) * (w u),  g = W_gate,e x, u = W_up,e x, w = the row's score (it stands on the expert's
 //             input; W (w x) = w (W x), so it is applied in 32-bit to the two accumulators),
-//   down:     y[row] = W_down,e act[row] as floats, or with one choice per token added into the token's output row.
+//   down:     y[row] = W_down,e act[row] as floats, or added into the token's output row: plainly with one choice per
+//             token, else by reductions in memory (the order of a token's choices, and with it the last bit of a sum of
+//             three or more, is not fixed; two addends onto zeros give the same sum in either order).
 //
 // A work item is (row tile of the table that moe_group wrote, tile of 128 output features). The table's length depends on
 // the routing and lives on the device: the grid is as large as the sizes allow (one CTA per SM at most) and every CTA reads
@@ -199,8 +201,10 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                             const float wg = s_wgt[quad][c + j];
                             const float g = v[j] * wg, up = u[j] * wg;
                             ((__nv_bfloat16*)out)[o] = __float2bfloat16(g / (1.0f + expf(-g)) * up);
-                        } else if (scatter) {
+                        } else if (scatter == 1) {
                             ((float*)out)[o] += v[j];       // one choice per token: nobody else writes this row
+                        } else if (scatter) {
+                            atomicAdd((float*)out + o, v[j]);   // a token's choices meet in its row, in no fixed order
                         } else {
                             ((float*)out)[o] = v[j];
                         }
@@ -322,13 +326,13 @@ NIB_API int nib_moe_gather_rows(const void* src, int lds, void* dst, int ldd, co
 
 // gate_up != 0: A = the rows in the grouped order [a_rows, K], W [experts, 2N, K] (gate rows, then up rows), out bfloat16
 // [a_rows, N]. Else: A [a_rows, K] in the grouped order, W [experts, N, K], out floats: [a_rows, N] in the grouped order, or
-// with scatter (one choice per token) added into the token's row of [tokens, N]. The table must have been made for row tiles
-// of `tile_rows` (32 or 128).
+// with scatter added into the token's row of [tokens, N] (1: plainly, one choice per token; 2: by reductions in memory).
+// The table must have been made for row tiles of `tile_rows` (32 or 128).
 NIB_API int nib_moe_gemm_tc(int gate_up, const void* A, int lda, int a_rows, const void* W, int experts, void* out, int ldo, const int* tiles,
                             const int* n_tiles, int max_tiles, const int* src_of, const float* sel_w, int top, int N, int K, int scatter,
                             int tile_rows, cudaStream_t stream) {
-    NIB_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && top > 0 && a_rows >= 0 && experts > 0 && max_tiles >= 0 && (!scatter || top == 1),
-                "experts (tensor cores): bad sizes");
+    NIB_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && top > 0 && a_rows >= 0 && experts > 0 && max_tiles >= 0 && scatter >= 0 && scatter <= 2
+                && (scatter != 1 || top == 1), "experts (tensor cores): bad sizes");
     NIB_REQUIRE(tile_rows == 32 || tile_rows == 128, "experts (tensor cores): row tiles of 32 or 128, not %d", tile_rows);
     if (max_tiles == 0 || a_rows == 0) return 0;
     const int w_rows = gate_up ? 2 * N : N;

@@ -116,10 +116,16 @@ class RoutedExperts(FeedForward):
     def forward(self, h, residual32: torch.Tensor, ctx: StepContext) -> None:
         h = as_tensor(h)
         m, dev = h.shape[0], h.device
-        z32 = torch.empty((m, self.experts), dtype=torch.float32, device=dev)
-        self.ops.linear(h, self.w_router, None, z32, "f32")
         chosen = torch.empty((m, self.top), dtype=torch.int32, device=dev)
         weight = torch.empty((m, self.top), dtype=torch.float32, device=dev)
+        # a short step (decoding): router, choice and grouping are one launch where the backend has one
+        step = getattr(self.ops, "moe_step", None)
+        plan = step(h, self.w_router, self.top, self.w_gate_up, self.w_down, chosen, weight) if step is not None else None
+        if plan is not None:
+            self.ops.moe_experts(h, chosen, weight, self.w_gate_up, self.w_down, residual32, plan=plan)
+            return
+        z32 = torch.empty((m, self.experts), dtype=torch.float32, device=dev)
+        self.ops.linear(h, self.w_router, None, z32, "f32")
         self.ops.moe_route(z32, self.top, chosen, weight)
         self.ops.moe_experts(h, chosen, weight, self.w_gate_up, self.w_down, residual32)
 

@@ -124,6 +124,42 @@ def test_experts_read_the_weighted_token(ops, dtype, m, hidden, ff, experts, top
         assert_close(slow - before, ref, dtype, "experts, CUDA cores")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,hidden,ff,experts,top", [(1, 32, 8, 1, 1), (8, 256, 64, 8, 2), (5, 72, 40, 33, 4), (16, 128, 24, 12, 1), (3, 100, 130, 6, 3),
+                                                     (64, 64, 16, 5, 2)])
+def test_a_short_step_routes_groups_and_gathers_in_one_launch(ops, dtype, m, hidden, ff, experts, top):
+    """Router, choice, grouping and gathered rows of a short step in one launch: the same choices and scores as the
+    separate steps, and the experts' result through its plan equals the plain loop."""
+    h = rnd(m, hidden, seed=1).to(dtype)
+    w = {"r.router": rnd(experts, hidden, seed=2, scale=hidden ** -0.5).to(dtype)}
+    for e in range(experts):
+        w[f"r.e{e}.gate"] = rnd(ff, hidden, seed=10 + 3 * e, scale=hidden ** -0.5).to(dtype)
+        w[f"r.e{e}.up"] = rnd(ff, hidden, seed=11 + 3 * e, scale=hidden ** -0.5).to(dtype)
+        w[f"r.e{e}.down"] = rnd(hidden, ff, seed=12 + 3 * e, scale=ff ** -0.5).to(dtype)
+    gate_up = torch.stack([torch.cat([w[f"r.e{e}.gate"], w[f"r.e{e}.up"]]) for e in range(experts)]).contiguous()
+    down = torch.stack([w[f"r.e{e}.down"] for e in range(experts)]).contiguous()
+    sel_e = torch.full((m, top), -1, dtype=torch.int32, device=DEV)
+    sel_w = torch.zeros(m, top, dtype=torch.float32, device=DEV)
+    plan = ops.moe_step(h, w["r.router"], top, gate_up, down, sel_e, sel_w)
+    assert plan is not None, "a step of these sizes fits one block"
+    s = torch.sigmoid(h.double().cpu() @ w["r.router"].double().cpu().t())
+    want = torch.topk(s, top, dim=-1)
+    assert torch.equal(sel_e.cpu().long(), want.indices)
+    assert_close(sel_w, want.values, torch.float32, "scores")
+    # the grouping: every entry has a row, rows of one expert are together, the tiles cover them
+    row_of, src_of = plan.row_of.cpu().long(), plan.src_of.cpu().long()
+    assert torch.equal(src_of[row_of], torch.arange(m * top))
+    by_row = sel_e.cpu().flatten()[src_of]
+    assert torch.equal(by_row, by_row.sort().values)
+    before = rnd(m, hidden, seed=3)
+    out = before.clone()
+    ops.moe_experts(h, sel_e, sel_w, gate_up, down, out, plan=plan)
+    mlp = {"router": {"experts": experts, "top": top}}
+    ref = plain.routed_experts(mlp, {k: v.double().cpu() for k, v in w.items()}, "r", h.double().cpu())
+    assert_close(out - before, ref, dtype, "experts of a short step")
+    assert ops.with_options(no_moe_step=True).moe_step(h, w["r.router"], top, gate_up, down, sel_e, sel_w) is None
+
+
 # ------------------------------------------------------------------------------------------ attention whose values are the keys
 def _prepared(ops, dtype, ctx, bt, page, num_pages, heads, kv, dim, qk, freq, rot, eps=1e-6):
     kp = torch.zeros(num_pages, kv, page, dim, dtype=dtype, device=DEV)
