@@ -286,29 +286,51 @@ latent_decode_mma_kernel(const __nv_bfloat16* __restrict__ qa, float* __restrict
     }
 }
 
-// Merges the splits of every (token, head) in split order. One warp per (token, head).
+// Merges the splits of every (token, head) in split order. One block per (token, head): every warp finds the maximum
+// and the denominator for itself (lanes over the splits) and keeps the splits' factors in shared memory; then a thread
+// owns an output column and adds the splits' parts in ascending order, eight loads in flight.
+constexpr int LM_FACTORS = 64;      // splits whose factors are kept; beyond, a factor is computed where it is used
+
 __global__ void __launch_bounds__(128)
 latent_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, float* __restrict__ out,
                              int rows, int splits, int dvp, int rank, const float* __restrict__ sink, int heads) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
-    const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    __shared__ float fac[4][LM_FACTORS];
+    const int w = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (w >= rows) return;
+    const float* ml = part_ml + (size_t)w * splits * 2;
     float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[((size_t)w * splits + s) * 2]);
+    for (int s = lane; s < splits; s += 32) m = fmaxf(m, ml[2 * s]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     const float sink2 = sink != nullptr ? sink[w % heads] * LOG2E : -INFINITY;
     m = fmaxf(m, sink2);        // the sink is one more part: a sum of exp(sink) at its own maximum, no output
-    float l = sink != nullptr ? exp2f(sink2 - m) : 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float ms = part_ml[((size_t)w * splits + s) * 2];
-        if (ms != -INFINITY) l += part_ml[((size_t)w * splits + s) * 2 + 1] * exp2f(ms - m);
+    float l = 0.f;
+    for (int s0 = 0; s0 < splits; s0 += 32) {       // lane sums in split order within its stride; the warp sum is a fixed tree
+        const int s = s0 + lane;
+        float f = 0.f;
+        if (s < splits) {
+            const float ms = ml[2 * s];
+            if (ms != -INFINITY) f = exp2f(ms - m);
+            l += ml[2 * s + 1] * f;
+            if (s < LM_FACTORS) fac[warp][s] = f;
+        }
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (sink != nullptr) l += exp2f(sink2 - m);
+    __syncwarp();
     const float inv = l > 0.f ? 1.0f / l : 0.f;
-    for (int d = lane; d < rank; d += 32) {
+    const float* po = part_o + (size_t)w * splits * dvp;
+    for (int d = threadIdx.x; d < rank; d += blockDim.x) {
         float acc = 0.f;
+#pragma unroll 8
         for (int s = 0; s < splits; ++s) {
-            const float ms = part_ml[((size_t)w * splits + s) * 2];
-            if (ms != -INFINITY) acc += part_o[((size_t)w * splits + s) * dvp + d] * exp2f(ms - m);
+            float f;
+            if (s < LM_FACTORS) f = fac[warp][s];
+            else { const float ms = ml[2 * s]; f = ms != -INFINITY ? exp2f(ms - m) : 0.f; }
+            acc = fmaf(po[(size_t)s * dvp + d], f, acc);
         }
         out[(size_t)w * rank + d] = acc * inv;
     }
@@ -337,7 +359,7 @@ int lm_launch(bool decode, const __nv_bfloat16* qa, float* out, const int* q_sta
     NIB_LAUNCH_CHECK();
     if (splits > 1) {
         const int rows = requests * heads;
-        NIB_CUDA(launch_pdl(latent_decode_combine_kernel, dim3(ceil_div(rows, 4)), dim3(128), (size_t)(0), stream, part_o, part_ml, out, rows, splits, DVP, rank, sink, heads));
+        NIB_CUDA(launch_pdl(latent_decode_combine_kernel, dim3(rows), dim3(128), (size_t)(0), stream, part_o, part_ml, out, rows, splits, DVP, rank, sink, heads));
         NIB_LAUNCH_CHECK();
     }
     return 0;

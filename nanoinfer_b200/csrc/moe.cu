@@ -113,22 +113,46 @@ moe_group_kernel(const int* __restrict__ sel_e, int n, int experts, int tile_row
 // choice, the grouping, and with `rows` the tokens' rows copied into the grouped order (what the tensor-core products read).
 constexpr int MOE_STEP_MAX_Z = 2048;     // tokens * experts
 
+// Sixteen bytes of a row as floats: 8 bfloat16 or 4 floats.
+__device__ __forceinline__ void unpack16(const uint4& u, const __nv_bfloat16*, float (&f)[8]) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 v = __bfloat1622float2(p[i]); f[2 * i] = v.x; f[2 * i + 1] = v.y; }
+}
+__device__ __forceinline__ void unpack16(const uint4& u, const float*, float (&f)[8]) {
+    f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y); f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
+    f[4] = f[5] = f[6] = f[7] = 0.f;
+}
+
+// `vec`: rows and bases are 16-byte aligned and the width is a multiple of 16 bytes, so rows move 16 bytes at a time.
 template <typename T>
 __global__ void __launch_bounds__(1024)
 moe_step_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ w_router, int tokens, int hidden, int experts, int top,
                 int* __restrict__ sel_e, float* __restrict__ sel_w, int tile_rows, int* __restrict__ row_of, int* __restrict__ src_of,
-                int* __restrict__ tiles, int* __restrict__ n_tiles, int max_tiles, T* __restrict__ rows) {
+                int* __restrict__ tiles, int* __restrict__ n_tiles, int max_tiles, T* __restrict__ rows, int vec) {
+    constexpr int V = 16 / (int)sizeof(T);
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
     __shared__ int cnt[MOE_MAX_EXPERTS], off[MOE_MAX_EXPERTS], toff[MOE_MAX_EXPERTS], cur[MOE_MAX_EXPERTS];
     __shared__ float z[MOE_STEP_MAX_Z];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
-    for (int p = warp; p < tokens * experts; p += warps) {      // a warp per (token, expert): ascending k within a lane
+    for (int p = warp; p < tokens * experts; p += warps) {      // a warp per (token, expert)
         const int t = p / experts, e = p - t * experts;
         const T* hr = h + (size_t)t * ldh;
         const T* wr = w_router + (size_t)e * hidden;
         float acc = 0.f;
-        for (int k = lane; k < hidden; k += 32) acc = fmaf(Elem<T>::load(hr + k), Elem<T>::load(wr + k), acc);
+        if (vec) {
+#pragma unroll 4
+            for (int k = lane * V; k < hidden; k += 32 * V) {
+                float a[8], b[8];
+                unpack16(__ldg(reinterpret_cast<const uint4*>(hr + k)), hr, a);
+                unpack16(__ldg(reinterpret_cast<const uint4*>(wr + k)), wr, b);
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc = fmaf(a[i], b[i], acc);
+            }
+        } else {
+            for (int k = lane; k < hidden; k += 32) acc = fmaf(Elem<T>::load(hr + k), Elem<T>::load(wr + k), acc);
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
         if (lane == 0) z[p] = acc;
@@ -141,9 +165,18 @@ moe_step_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ w_router
     group_entries(sel_e, n, experts, tile_rows, row_of, src_of, tiles, n_tiles, max_tiles, cnt, off, toff, cur);
     if (rows == nullptr) return;
     __syncthreads();
-    for (int i = tid; i < n * hidden; i += blockDim.x) {
-        const int r = i / hidden, c = i - r * hidden;
-        rows[(size_t)r * hidden + c] = h[(size_t)(src_of[r] / top) * ldh + c];
+    if (vec) {
+        const int per_row = hidden / V;
+#pragma unroll 4
+        for (int i = tid; i < n * per_row; i += blockDim.x) {
+            const int r = i / per_row, c = (i - r * per_row) * V;
+            *reinterpret_cast<uint4*>(rows + (size_t)r * hidden + c) = __ldg(reinterpret_cast<const uint4*>(h + (size_t)(src_of[r] / top) * ldh + c));
+        }
+    } else {
+        for (int i = tid; i < n * hidden; i += blockDim.x) {
+            const int r = i / hidden, c = i - r * hidden;
+            rows[(size_t)r * hidden + c] = h[(size_t)(src_of[r] / top) * ldh + c];
+        }
     }
 }
 
@@ -305,13 +338,15 @@ NIB_API int nib_moe_step(const void* h, int ldh, const void* w_router, int token
     NIB_REQUIRE(nib_moe_step_supported(tokens, hidden, experts, top) == 1 && ldh >= hidden && tile_rows > 0
                 && max_tiles >= nib_moe_max_tiles(tokens * top, experts, tile_rows), "moe_step: bad sizes");
     NIB_REQUIRE(dtype == NIB_F32 || dtype == NIB_BF16, "moe_step: unknown dtype %d", dtype);
+    const int per16 = dtype == NIB_F32 ? 4 : 8;
+    const int vec = (hidden % per16 == 0 && ldh % per16 == 0 && (((uintptr_t)h | (uintptr_t)w_router | (uintptr_t)rows) & 15) == 0) ? 1 : 0;
     if (dtype == NIB_F32)
         NIB_CUDA(launch_pdl(moe_step_kernel<float>, dim3(1), dim3(1024), (size_t)0, stream, (const float*)h, ldh, (const float*)w_router, tokens, hidden,
-                            experts, top, sel_e, sel_w, tile_rows, row_of, src_of, tiles, n_tiles, max_tiles, (float*)rows));
+                            experts, top, sel_e, sel_w, tile_rows, row_of, src_of, tiles, n_tiles, max_tiles, (float*)rows, vec));
     else
         NIB_CUDA(launch_pdl(moe_step_kernel<__nv_bfloat16>, dim3(1), dim3(1024), (size_t)0, stream, (const __nv_bfloat16*)h, ldh,
                             (const __nv_bfloat16*)w_router, tokens, hidden, experts, top, sel_e, sel_w, tile_rows, row_of, src_of, tiles, n_tiles,
-                            max_tiles, (__nv_bfloat16*)rows));
+                            max_tiles, (__nv_bfloat16*)rows, vec));
     NIB_LAUNCH_CHECK();
     return 0;
 }
