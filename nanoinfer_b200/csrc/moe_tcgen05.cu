@@ -47,12 +47,23 @@ template <int TOK, bool DUAL> struct Cfg {
     static_assert(2 * ACC_COLS <= 512, "two accumulator buffers must fit the 512 TMEM columns");
 };
 
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&v);
+}
+
 template <int TOK, bool GATE_UP>
 __global__ void __launch_bounds__(THREADS, 1)
 moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, void* __restrict__ out, int ldo,
               const int* __restrict__ tiles, const int* __restrict__ n_tiles, int max_tiles, const int* __restrict__ src_of,
               const float* __restrict__ sel_w, int top, int n_out, int k_dim, int w_rows, int scatter) {
     constexpr bool DUAL = GATE_UP;
+    // Row tiles of 128: the operands change places, so the ROWS are the instruction's M side (the TMEM lanes) and the 128
+    // features its columns; a thread of the epilogue then owns a row and writes 16 consecutive features at a time.
+    constexpr bool SWAP = (TOK == BLOCK_F);
     using C = Cfg<TOK, DUAL>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -120,7 +131,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer
-        constexpr unsigned idesc = instr_desc(BLOCK_F, TOK);
+        constexpr unsigned idesc = SWAP ? instr_desc(TOK, BLOCK_F) : instr_desc(BLOCK_F, TOK);
         int it = 0, local = 0;
         for (int item = blockIdx.x; item < items && !s_failed; item += gridDim.x, ++local) {
             const int buf = local & 1;
@@ -148,8 +159,13 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                 for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                     const unsigned long long adv = (unsigned long long)((k * UMMA_K * 2) >> 4);   // 32 bytes per step
                     const bool accumulate = (kb > 0) || (k > 0);
-                    tc_mma(acc, w_desc + adv, a_desc + adv, idesc, accumulate);
-                    if (DUAL) tc_mma(acc + TOK, u_desc + adv, a_desc + adv, idesc, accumulate);
+                    if (SWAP) {
+                        tc_mma(acc, a_desc + adv, w_desc + adv, idesc, accumulate);
+                        if (DUAL) tc_mma(acc + BLOCK_F, a_desc + adv, u_desc + adv, idesc, accumulate);
+                    } else {
+                        tc_mma(acc, w_desc + adv, a_desc + adv, idesc, accumulate);
+                        if (DUAL) tc_mma(acc + TOK, u_desc + adv, a_desc + adv, idesc, accumulate);
+                    }
                 }
                 tc_commit(&empty_bar[s]);        // the stage is free when these MMAs have read it
             }
@@ -165,6 +181,85 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             const int tile = item / f_tiles, f0 = (item - tile * f_tiles) * BLOCK_F;
             const int row0 = __ldg(tiles + 3 * tile + 1), rows = min(TOK, __ldg(tiles + 3 * tile + 2));
             const int f = f0 + quad * 32 + lane;
+            if constexpr (SWAP) {
+                // ---- this thread owns row row0 + t of the tile; its lane holds the tile's 128 features
+                const int t = quad * 32 + lane;
+                const bool live = t < rows;
+                float wg = 0.f;
+                size_t orow = 0;
+                if (live) {
+                    const int entry = __ldg(src_of + row0 + t);
+                    wg = __ldg(sel_w + entry);
+                    orow = (size_t)((!GATE_UP && scatter) ? entry / top : row0 + t) * ldo;
+                }
+                bool ok = !s_failed && mbar_wait(&acc_full_bar[buf], (local >> 1) & 1);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    if (lane == 0 && !s_failed) { atomicCAS(&g_moe_tc_error, 0, (3 << 16) | (int)blockIdx.x); s_failed = 1; }
+                    break;
+                }
+                tc_fence_after();
+                const unsigned lane_addr = tmem_base + buf * C::ACC_COLS + ((unsigned)(quad * 32) << 16);
+#pragma unroll 1
+                for (int c = 0; c < BLOCK_F; c += 16) {
+                    if (f0 + c >= n_out) break;
+                    unsigned rv[16], ru[16];
+                    tmem_ld16_async(lane_addr + c, rv);
+                    if (DUAL) tmem_ld16_async(lane_addr + BLOCK_F + c, ru);
+                    tmem_wait_ld();
+                    if (!live) continue;
+                    float x[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (GATE_UP) {
+                            const float g = __uint_as_float(rv[j]) * wg, up = __uint_as_float(ru[j]) * wg;
+                            x[j] = __fdividef(g, 1.0f + __expf(-g)) * up;      // the dense gated product's epilogue has the same forms
+                        } else {
+                            x[j] = __uint_as_float(rv[j]);
+                        }
+                    }
+                    const int f = f0 + c;
+                    const bool whole = f + 16 <= n_out;       // 16 features: 32 bytes of bfloat16 or 64 of floats, aligned
+                    if (GATE_UP) {
+                        __nv_bfloat16* o = (__nv_bfloat16*)out + orow + f;
+                        if (whole) {
+                            uint4 p0, p1;
+                            p0.x = pack_bf16(x[0], x[1]); p0.y = pack_bf16(x[2], x[3]); p0.z = pack_bf16(x[4], x[5]); p0.w = pack_bf16(x[6], x[7]);
+                            p1.x = pack_bf16(x[8], x[9]); p1.y = pack_bf16(x[10], x[11]); p1.z = pack_bf16(x[12], x[13]); p1.w = pack_bf16(x[14], x[15]);
+                            reinterpret_cast<uint4*>(o)[0] = p0;
+                            reinterpret_cast<uint4*>(o)[1] = p1;
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) if (f + j < n_out) o[j] = __float2bfloat16(x[j]);
+                        }
+                    } else {
+                        float* o = (float*)out + orow + f;
+                        if (whole && scatter == 2) {
+#pragma unroll
+                            for (int j = 0; j < 16; j += 4) red_add_v4(o + j, x[j], x[j + 1], x[j + 2], x[j + 3]);
+                        } else if (whole) {
+#pragma unroll
+                            for (int j = 0; j < 16; j += 4) {
+                                float4 cur = scatter ? *reinterpret_cast<float4*>(o + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                                cur.x += x[j]; cur.y += x[j + 1]; cur.z += x[j + 2]; cur.w += x[j + 3];
+                                *reinterpret_cast<float4*>(o + j) = cur;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                if (f + j >= n_out) break;
+                                if (scatter == 2) atomicAdd(o + j, x[j]);
+                                else if (scatter) o[j] += x[j];
+                                else o[j] = x[j];
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty_bar[buf]);
+                continue;
+            }
             // what the epilogue reads besides the accumulator is fetched while the tensor core still works on the tile
             __syncwarp();
             for (int c = lane; c < TOK; c += 32) {
@@ -200,7 +295,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                         if (GATE_UP) {
                             const float wg = s_wgt[quad][c + j];
                             const float g = v[j] * wg, up = u[j] * wg;
-                            ((__nv_bfloat16*)out)[o] = __float2bfloat16(g / (1.0f + expf(-g)) * up);
+                            ((__nv_bfloat16*)out)[o] = __float2bfloat16(__fdividef(g, 1.0f + __expf(-g)) * up);
                         } else if (scatter == 1) {
                             ((float*)out)[o] += v[j];       // one choice per token: nobody else writes this row
                         } else if (scatter) {
