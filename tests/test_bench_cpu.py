@@ -77,3 +77,20 @@ def test_launches_are_sorted_into_the_parts_of_a_layer():
     assert n["kinds"]["qkv"] == 1152 * 896 and n["kinds"]["gate_up"] == 2 * 896 * 4864
     assert sum(n["kinds"][k] for k in ("qkv", "o_proj", "gate_up", "down")) == n["per_layer_params"]
     assert n["kv_bytes_per_token_layer"] * 24 == n["kv_bytes_per_token"]
+
+
+def test_the_designs_bench_sizes_are_configurations_the_registry_takes():
+    """``--design darotar``: both models of a size are valid configurations of equal width, depth and vocabulary, and a
+    token passes through as many feed-forward parameters in both (``top`` experts, each ``1 / top`` of the dense one)."""
+    from nanoinfer_b200.registry import config_from_json_dict, plan_for
+    for size in bench.DAROTAR_SIZES.values():
+        dar, dense = bench.darotar_configs(size)
+        plan, dense_plan = plan_for(config_from_json_dict(dar)), plan_for(config_from_json_dict(dense))
+        assert len(plan.layers) == len(dense_plan.layers) == size["layers"]
+        assert plan.hidden_size == dense_plan.hidden_size == size["width"] and plan.vocab_size == dense_plan.vocab_size
+        kinds = [layer["type"] for layer in dar["layers"]]
+        assert kinds.count("attention") == kinds.count("latent_attention") == size["layers"] // 2
+        readers = [i for i, layer in enumerate(dar["layers"]) if layer["mixer"].get("kv_from") is not None]
+        assert readers and all(dar["layers"][dar["layers"][i]["mixer"]["kv_from"]]["type"] == "latent_attention" for i in readers)
+        mlp = dar["layers"][0]["mlp"]
+        assert mlp["router"]["top"] * mlp["expert"]["ff"] == size["ff_swiglu"]
