@@ -525,7 +525,7 @@ NIB_API int nib_gated_norm(const float* o, int ldo, const float* gate, int ldg, 
 template <typename T, int THREADS>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_add_kernel(float* __restrict__ y, const float* __restrict__ gain, float* __restrict__ x, T* __restrict__ h_out,
-                   int rows, int width, float eps, float mult, int clear) {
+                   int rows, int width, float eps, float mult, int clear, int vec) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
     __shared__ float part[THREADS / 32];
@@ -537,7 +537,14 @@ rmsnorm_add_kernel(float* __restrict__ y, const float* __restrict__ gain, float*
     float* yr = y + (size_t)row * width;
     float* xr = x + (size_t)row * width;
     float ss = 0.f;
-    for (int c = first; c < width; c += step) ss = fmaf(yr[c], yr[c], ss);
+    if (vec) {      // rows of whole 16-byte groups: four elements a load
+        for (int c = first * 4; c < width; c += step * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(yr + c);
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+    } else {
+        for (int c = first; c < width; c += step) ss = fmaf(yr[c], yr[c], ss);
+    }
     ss = warp_sum(ss);
     if (BLOCK_ROW) {
         if (lane == 0) part[warp] = ss;
@@ -546,6 +553,28 @@ rmsnorm_add_kernel(float* __restrict__ y, const float* __restrict__ gain, float*
         for (int w = 0; w < THREADS / 32; ++w) ss += part[w];      // the same order in every thread
     }
     const float scale = mult / sqrtf(ss / (float)width + eps);
+    if (vec) {
+        for (int c = first * 4; c < width; c += step * 4) {
+            const float4 yv = *reinterpret_cast<const float4*>(yr + c), g = __ldg(reinterpret_cast<const float4*>(gain + c));
+            float4 v = *reinterpret_cast<const float4*>(xr + c);
+            v.x += yv.x * scale * g.x; v.y += yv.y * scale * g.y; v.z += yv.z * scale * g.z; v.w += yv.w * scale * g.w;
+            *reinterpret_cast<float4*>(xr + c) = v;
+            if (h_out != nullptr) {
+                T* ho = h_out + (size_t)row * width + c;
+                if constexpr (sizeof(T) == 4) {
+                    *reinterpret_cast<float4*>(ho) = v;
+                } else {
+                    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<const unsigned*>(&lo);
+                    pk.y = *reinterpret_cast<const unsigned*>(&hi);
+                    *reinterpret_cast<uint2*>(ho) = pk;
+                }
+            }
+            if (clear) *reinterpret_cast<float4*>(yr + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        return;
+    }
     for (int c = first; c < width; c += step) {
         const float v = xr[c] + yr[c] * scale * gain[c];
         xr[c] = v;
@@ -560,8 +589,9 @@ NIB_API int nib_rmsnorm_add(float* y, const float* gain, float* x, void* h_out, 
     NIB_REQUIRE(dtype == NIB_F32 || dtype == NIB_BF16, "rmsnorm_add: unknown dtype %d", dtype);
     if (rows == 0) return 0;
     const bool block_row = rows <= 64 && width >= 512;
+    const int vec = (width % 4 == 0 && (((uintptr_t)y | (uintptr_t)gain | (uintptr_t)x | (uintptr_t)h_out) & 15) == 0) ? 1 : 0;
 #define NIB_RA(T, THREADS, GRID) \
-    NIB_CUDA(launch_pdl(rmsnorm_add_kernel<T, THREADS>, dim3(GRID), dim3(THREADS), (size_t)0, stream, y, gain, x, (T*)h_out, rows, width, eps, mult, clear))
+    NIB_CUDA(launch_pdl(rmsnorm_add_kernel<T, THREADS>, dim3(GRID), dim3(THREADS), (size_t)0, stream, y, gain, x, (T*)h_out, rows, width, eps, mult, clear, vec))
     if (block_row) {
         if (dtype == NIB_F32) NIB_RA(float, 256, rows); else NIB_RA(__nv_bfloat16, 256, rows);
     } else {
