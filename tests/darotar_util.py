@@ -95,8 +95,8 @@ def pin_routing(cfg, classes=8):
     """A change of the random tensors after which the routing is the same in every precision: the first ``classes``
     channels of the stream hold a one-hot class of the token (token id modulo ``classes``), no branch ever adds to them
     (the gains of every norm are zero there), and the routers read nothing else. Every router logit is then one product
-    of two numbers that bfloat16 holds, equal in 16, 32 and 64 bits, so a comparison of bfloat16 logits with the plain
-    implementation cannot rest on a close call between two experts (in 32-bit the tests keep the random routers).
+    of two numbers that bfloat16 holds, equal in 16, 32 and 64 bits, and an expert's logits lie a sixteenth apart, so a
+    comparison of bfloat16 logits with the plain implementation cannot rest on a close call or a tie between two experts (in 32-bit the tests keep the random routers).
     The experts still read the whole stream, each token scaled by its score."""
     def change(t):
         emb = t["embed"]
@@ -108,7 +108,11 @@ def pin_routing(cfg, classes=8):
                 t[f"l{i}.norm2"][:classes] = 0
                 r = t[f"l{i}.mlp.router"]
                 r[:, classes:] = 0
-                r[:, :classes] = (torch.randn(r.shape[0], classes, generator=torch.Generator().manual_seed(100 + i)) * 0.6).to(r.dtype)
+                # per class the experts in a random order, a sixteenth apart: numbers that bfloat16 holds, no two equal
+                g = torch.Generator().manual_seed(100 + i)
+                for c in range(classes):
+                    order = torch.randperm(r.shape[0], generator=g).float()
+                    r[:, c] = ((order - (r.shape[0] - 1) / 2) / 16).to(r.dtype)
     return change
 
 

@@ -551,7 +551,8 @@ def test_the_first_token_reaches_the_logits_through_the_latent_rows(tmp_path):
 
 
 @pytest.mark.parametrize("seed,dtype", [(300, "float32"), (301, "float32"), (302, "float32"), (303, "float32"), (304, "float32"), (305, "float32"),
-                                        (306, "float32"), (307, "float32"), (301, "bfloat16"), (303, "bfloat16"), (306, "bfloat16")])
+                                        (306, "float32"), (307, "float32"), (301, "bfloat16"), (303, "bfloat16"), (306, "bfloat16"),
+                                        (449, "float32"), (449, "bfloat16"), (453, "bfloat16")])
 def test_random_configurations(seed, dtype, tmp_path):
     """Layer orders, sizes and constants drawn at random (one head, a window of 1, one expert, all experts chosen, widths
     that no vector path takes ...): a prompt in portions with a decoded tail beside a second request, against the plain
