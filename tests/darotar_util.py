@@ -183,3 +183,49 @@ def random_config(rng):
                              rng.choice([5, 16, 24, 64]), rank, base, scale=rng.choice([None, 0.15]), kv_from=src, mlp=mlp))
     return {"architecture": "Darotar", "vocab": rng.choice([50, 131, 257, 1000]), "width": width,
             "norm": {"eps": rng.choice([1e-6, 1e-5, 1e-4])}, "residual_mult": rng.choice([0.25, 0.5, 1.0, 1.5]), "layers": layers}
+
+
+def larger_config(rng):
+    """A configuration at sizes of a small real model: widths of 128 to 384, heads of 32 to 128, 4 to 16 experts."""
+    width = rng.choice([128, 192, 256, 320, 384])
+    layers, owners = [], []
+    for i in range(rng.randint(3, 8)):
+        e = rng.choice([4, 8, 10, 16])
+        mlp = rng.choice([None, 1, 1, 1]) and moe(e, rng.choice([1, 2, 3]), rng.choice([32, 64, 128]))
+        if rng.random() < 0.45:
+            kv = rng.choice([1, 2, 4]); dim = rng.choice([32, 64, 96, 128])
+            layers.append(attention(kv * rng.choice([1, 2, 4]), kv, dim, rng.choice([dim, dim // 2, 16]), rng.choice([1e4, 2e4, 1e6]),
+                                    factor=rng.choice([None, 2.0, 4.0, 8.0]), window=rng.choice([16, 48, 64, 96, 100, 128]), scale=rng.choice([None, 0.15]), mlp=mlp))
+            continue
+        src = rng.choice(owners) if owners and rng.random() < 0.45 else None
+        if src is None:
+            rank, rdim, base = rng.choice([32, 64, 96, 128]), rng.choice([8, 16, 32, 64]), rng.choice([1e4, 1e6])
+            owners.append(i)
+        else:
+            o = layers[src]["mixer"]; rank, rdim, base = o["kv_rank"], o["rot_dim"], o["rot"]["base"]
+        layers.append(latent(rng.choice([2, 4, 8, 16]), rng.choice([16, 32, 64]), rdim, rng.choice([16, 32, 64]), rng.choice([48, 72, 128]), rank, base,
+                             scale=rng.choice([None, 0.14]), kv_from=src, mlp=mlp))
+    return {"architecture": "Darotar", "vocab": rng.choice([500, 1000]), "width": width, "norm": {"eps": 1e-6},
+            "residual_mult": rng.choice([0.5, 0.7, 1.0]), "layers": layers}
+
+
+def mixed_schedule(rng, lens):
+    """Steps of [(request, count)]: at most four live, each request first in portions, its last tokens one by one."""
+    pending, live, at, steps = list(range(len(lens))), [], {}, []
+    while pending or live:
+        while pending and len(live) < 4 and (not live or rng.random() < 0.6):
+            r = pending.pop(0); live.append(r); at[r] = 0
+        step = []
+        for r in list(live):
+            if rng.random() < 0.15 and len(live) > 1:
+                continue        # left out of this step
+            left = lens[r] - at[r]
+            c = 1 if left <= 20 else min(left - 20, rng.choice([2, 3, 7, 16, 33, 64, 100]))
+            step.append((r, c)); at[r] += c
+            if at[r] == lens[r]:
+                live.remove(r)
+        if step:
+            steps.append(step)
+    return steps
+
+

@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import plain_darotar as plain
-from darotar_util import CFG_A, CFG_B, CFG_C, assert_within_rounding, attention, latent, moe, pin_routing, plain_logits, random_config, tokens, write_model
+from darotar_util import CFG_A, CFG_B, CFG_C, assert_within_rounding, attention, larger_config, latent, mixed_schedule, moe, pin_routing, plain_logits, random_config, tokens, write_model
 from gpu_util import assert_close
 from torch_ops import TorchOps
 
@@ -582,6 +582,42 @@ def test_random_configurations(seed, dtype, tmp_path):
     judge(d, dtype)(torch.cat(got2), ref2[:pos2], other, "second request")
     eng.check_device()
     eng.cache.check()
+
+
+@pytest.mark.parametrize("seed,dtype", [(21, "float32"), (21, "bfloat16"), (34, "float32"), (34, "bfloat16"), (47, "bfloat16")])
+def test_larger_configurations_under_a_mixed_schedule(seed, dtype, tmp_path):
+    """Six requests of 60 to 230 tokens, at most four live: portions of 2 to 100 tokens beside single tokens, requests left out of a
+    step, slots and pages given back and used again in a pool made for four; sizes of a small real model (tensor-core paths of
+    every kernel in bfloat16). Every position of every request against the plain implementation."""
+    from nanoinfer_b200.engine import StepEntry
+    rng = random.Random(seed)
+    cfg = larger_config(rng)
+    lens = [rng.randint(60, 230) for _ in range(6)]
+    seqs = [tokens(n, cfg["vocab"], seed * 10 + i) for i, n in enumerate(lens)]
+    plan = mixed_schedule(rng, lens)
+    assert max(len(step) for step in plan) == 4 and any(c > 1 for step in plan for _, c in step if len(step) > 1)
+    page = rng.choice([16, 64])
+    d = write_model(str(tmp_path), cfg, seed, weights=None if dtype == "float32" else pin_routing(cfg))
+    eng = gpu_engine(d, dtype, page=page, pages=4 * (-(-max(lens) // page) + 1) + 2, slots=4)
+    got, at, live = {i: [] for i in range(6)}, {i: 0 for i in range(6)}, {}
+    for step in plan:
+        entries = []
+        for r, c in step:
+            if r not in live:
+                live[r] = eng.open(f"r{r}")
+            entries.append(StepEntry(live[r], seqs[r][at[r]:at[r] + c], list(range(c))))
+        logits = eng.step(entries).clone()
+        row = 0
+        for r, c in step:
+            got[r].append(logits[row:row + c])
+            row += c
+            at[r] += c
+            if at[r] == lens[r]:
+                eng.close(live.pop(r))
+        eng.cache.check()
+    eng.check_device()
+    for r in range(6):
+        judge(d, dtype)(torch.cat(got[r]), plain_logits(d, seqs[r]), seqs[r], f"request {r}")
 
 
 def test_trace_replay_as_a_child_process(folders, tmp_path):
