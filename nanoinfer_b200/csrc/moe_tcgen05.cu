@@ -59,7 +59,7 @@ template <int TOK, bool GATE_UP>
 __global__ void __launch_bounds__(THREADS, 1)
 moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, void* __restrict__ out, int ldo,
               const int* __restrict__ tiles, const int* __restrict__ n_tiles, int max_tiles, const int* __restrict__ src_of,
-              const float* __restrict__ sel_w, int top, int n_out, int k_dim, int w_rows, int scatter) {
+              const float* __restrict__ sel_w, int top, int n_out, int k_dim, int w_rows, int scatter, int splits, int kb_per_split) {
     constexpr bool DUAL = GATE_UP;
     // Row tiles of 128: the operands change places, so the ROWS are the instruction's M side (the TMEM lanes) and the 128
     // features its columns; a thread of the epilogue then owns a row and writes 16 consecutive features at a time.
@@ -100,16 +100,21 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
     pdl_wait();         // from here on the kernel reads what earlier kernels wrote (the table, the rows)
     int nt = __ldcg(n_tiles);
     if (nt > max_tiles) nt = max_tiles;
-    const int items = nt * f_tiles;      // work item = (row tile, feature tile), feature tiles fastest
+    // work item = (row tile, feature tile, split of K), splits fastest, then feature tiles. With K split (the down product
+    // of a short step, whose tiles alone leave SMs idle) every item adds its partial sums into the output by reductions.
+    const int items = nt * f_tiles * splits;
+    const bool reduce = scatter == 2 || splits > 1;
 
     if (warp == 0 && lane == 0) {
         // ---------------- producer: TMA loads of the expert's weight rows and of the tile's rows, stage after stage
         int it = 0, issued = 0;
         for (int item = blockIdx.x; item < items && !s_failed; item += gridDim.x) {
-            const int tile = item / f_tiles, f0 = (item - tile * f_tiles) * BLOCK_F;
+            const int split = item % splits, rest = item / splits;
+            const int tile = rest / f_tiles, f0 = (rest - tile * f_tiles) * BLOCK_F;
             const int expert = __ldg(tiles + 3 * tile), row0 = __ldg(tiles + 3 * tile + 1);
             const int wrow = expert * w_rows + f0;
-            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            const int kb_end = min(k_blocks, (split + 1) * kb_per_split);
+            for (int kb = split * kb_per_split; kb < kb_end; ++kb, ++it) {
                 const int s = it % C::STAGES;
                 if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1)) {
                     atomicCAS(&g_moe_tc_error, 0, (1 << 16) | (int)blockIdx.x);
@@ -143,7 +148,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             }
             tc_fence_after();
             const unsigned acc = tmem_base + buf * C::ACC_COLS;
-            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            const int kb_begin = (item % splits) * kb_per_split, kb_end = min(k_blocks, kb_begin + kb_per_split);
+            for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
                 const int s = it % C::STAGES;
                 if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1)) {
                     atomicCAS(&g_moe_tc_error, 0, (2 << 16) | (int)blockIdx.x);
@@ -158,7 +164,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
 #pragma unroll
                 for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                     const unsigned long long adv = (unsigned long long)((k * UMMA_K * 2) >> 4);   // 32 bytes per step
-                    const bool accumulate = (kb > 0) || (k > 0);
+                    const bool accumulate = (kb > kb_begin) || (k > 0);
                     if (SWAP) {
                         tc_mma(acc, a_desc + adv, w_desc + adv, idesc, accumulate);
                         if (DUAL) tc_mma(acc + BLOCK_F, a_desc + adv, u_desc + adv, idesc, accumulate);
@@ -178,7 +184,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
         int local = 0;
         for (int item = blockIdx.x; item < items; item += gridDim.x, ++local) {
             const int buf = local & 1;
-            const int tile = item / f_tiles, f0 = (item - tile * f_tiles) * BLOCK_F;
+            const int rest = item / splits;
+            const int tile = rest / f_tiles, f0 = (rest - tile * f_tiles) * BLOCK_F;
             const int row0 = __ldg(tiles + 3 * tile + 1), rows = min(TOK, __ldg(tiles + 3 * tile + 2));
             const int f = f0 + quad * 32 + lane;
             if constexpr (SWAP) {
@@ -234,7 +241,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                         }
                     } else {
                         float* o = (float*)out + orow + f;
-                        if (whole && scatter == 2) {
+                        if (whole && reduce) {
 #pragma unroll
                             for (int j = 0; j < 16; j += 4) red_add_v4(o + j, x[j], x[j + 1], x[j + 2], x[j + 3]);
                         } else if (whole) {
@@ -248,7 +255,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
 #pragma unroll
                             for (int j = 0; j < 16; ++j) {
                                 if (f + j >= n_out) break;
-                                if (scatter == 2) atomicAdd(o + j, x[j]);
+                                if (reduce) atomicAdd(o + j, x[j]);
                                 else if (scatter) o[j] += x[j];
                                 else o[j] = x[j];
                             }
@@ -296,10 +303,10 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                             const float wg = s_wgt[quad][c + j];
                             const float g = v[j] * wg, up = u[j] * wg;
                             ((__nv_bfloat16*)out)[o] = __float2bfloat16(__fdividef(g, 1.0f + __expf(-g)) * up);
-                        } else if (scatter == 1) {
-                            ((float*)out)[o] += v[j];       // one choice per token: nobody else writes this row
+                        } else if (reduce) {
+                            atomicAdd((float*)out + o, v[j]);   // a token's choices, or the splits of K, meet in its row in no fixed order
                         } else if (scatter) {
-                            atomicAdd((float*)out + o, v[j]);   // a token's choices meet in its row, in no fixed order
+                            ((float*)out)[o] += v[j];       // one choice per token: nobody else writes this row
                         } else {
                             ((float*)out)[o] = v[j];
                         }
@@ -373,17 +380,22 @@ int sm_count() {
 
 template <int TOK, bool GATE_UP>
 int launch_moe_tc(const CUtensorMap& mw, const CUtensorMap& ma, void* out, int ldo, const int* tiles, const int* n_tiles, int max_tiles,
-                  const int* src_of, const float* sel_w, int top, int N, int K, int w_rows, int scatter, cudaStream_t stream) {
+                  const int* src_of, const float* sel_w, int top, int N, int K, int w_rows, int scatter, int splits, cudaStream_t stream) {
     using C = Cfg<TOK, GATE_UP>;
     static bool configured = false;
     if (!configured) {
         NIB_CUDA(cudaFuncSetAttribute(moe_tc_kernel<TOK, GATE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         configured = true;
     }
-    const long long most = (long long)max_tiles * ceil_div(N, BLOCK_F);
+    const int k_blocks = ceil_div(K, BLOCK_K);
+    if (splits < 1 || GATE_UP || scatter == 0) splits = 1;      // only sums into the output can be split along K
+    if (splits > k_blocks) splits = k_blocks;
+    const int kb_per_split = ceil_div(k_blocks, splits);
+    splits = ceil_div(k_blocks, kb_per_split);               // no split without work
+    const long long most = (long long)max_tiles * ceil_div(N, BLOCK_F) * splits;
     const int sms = sm_count();
     NIB_CUDA(launch_pdl(moe_tc_kernel<TOK, GATE_UP>, dim3((unsigned)(most < sms ? most : sms)), dim3(THREADS), (size_t)C::SMEM, stream, mw, ma, out, ldo,
-                        tiles, n_tiles, max_tiles, src_of, sel_w, top, N, K, w_rows, scatter));
+                        tiles, n_tiles, max_tiles, src_of, sel_w, top, N, K, w_rows, scatter, splits, kb_per_split));
     return 0;
 }
 
@@ -445,7 +457,17 @@ NIB_API int nib_moe_gemm_tc(int gate_up, const void* A, int lda, int a_rows, con
         }
     }
     if (make_map(&ma, A, a_rows, K, lda, tile_rows)) return 1;
-#define NIB_MT(TOK, GU) launch_moe_tc<TOK, GU>(mw, ma, out, ldo, tiles, n_tiles, max_tiles, src_of, sel_w, top, N, K, w_rows, scatter, stream)
+    // A short step's down product: its tiles (about one per expert in use, times the feature tiles) leave SMs idle and each is a
+    // long walk over K; K is split so that about as many items as SMs stream the weights, none shorter than four stages.
+    int splits = 1;
+    if (!gate_up && scatter && tile_rows == 32) {
+        const long long tiles_est = (long long)(a_rows < experts ? a_rows : experts) * ceil_div(N, BLOCK_F);
+        const int sms = sm_count(), k_blocks = ceil_div(K, BLOCK_K);
+        if (tiles_est * 2 <= sms) splits = (int)(sms / tiles_est);
+        if (splits > k_blocks / 4) splits = k_blocks / 4;
+        if (splits < 1) splits = 1;
+    }
+#define NIB_MT(TOK, GU) launch_moe_tc<TOK, GU>(mw, ma, out, ldo, tiles, n_tiles, max_tiles, src_of, sel_w, top, N, K, w_rows, scatter, splits, stream)
     int rc;
     if (tile_rows == 32) rc = gate_up ? NIB_MT(32, true) : NIB_MT(32, false);
     else rc = gate_up ? NIB_MT(128, true) : NIB_MT(128, false);
