@@ -8,19 +8,23 @@
 //    k head divided by its root mean square once more, without a gain (a norm AFTER the rotation), queries written in the
 //    storage type, keys and values written into their pages. Keys are `dk` wide, values `dv`; the values may be the keys
 //    as projected (before norm and rotation), the rows then hold [q | k] only. One warp per (token, head of q, k or v).
+//    With FXP_NORM_WHOLE the root mean square is taken over ALL heads of a token's q (and of its k) at once and the gain
+//    has the size of the whole projection. With `v_first` a value becomes (1 - lambda) v + lambda v_first, where v_first
+//    holds the same token's values of another layer (32-bit rows) and lambda = vmix[0]; the blend is what is cached.
 //  * attention_flex: one warp per (token, query head). A query at position p of its request sees the keys j <= p,
 //    with a window only j > p - window, with a chunk only floor(j / chunk) == floor(p / chunk) (counted from the
 //    request's position 0). score = (q . k) * scale; with a cap c: c tanh(score / c); with slopes: minus
 //    slope[head] * (p - j). Keys are taken in blocks of 32 that start at absolute multiples of 32 with a running
 //    maximum and sum, so a position's result does not depend on how the request was cut into steps, nor on what else
-//    is in the batch. The output (dv wide per head) is multiplied by out_scale and written as float or T.
+//    is in the batch. With `sinks` the softmax's denominator holds exp(sinks[head]) once more: a term without key and
+//    value, neither scaled nor capped. The output (dv wide per head) is multiplied by out_scale and written as float or T.
 #include "common.cuh"
 
 constexpr int FX_MAX_D = 256;
 constexpr int FX_WARPS = 4;
 
 // flags of attention_prepare
-enum { FXP_INTERLEAVED = 1, FXP_UNIT_NORM_AFTER = 2, FXP_VALUES_ARE_KEYS = 4 };
+enum { FXP_INTERLEAVED = 1, FXP_UNIT_NORM_AFTER = 2, FXP_VALUES_ARE_KEYS = 4, FXP_NORM_WHOLE = 8 };
 
 template <typename T>
 __global__ void __launch_bounds__(FX_WARPS * 32)
@@ -28,7 +32,8 @@ attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ 
                          const float* __restrict__ k_gain, float eps, const float* __restrict__ freq, int rot,
                          const int* __restrict__ positions, const int* __restrict__ req_index, const int* __restrict__ block_table,
                          int bt_stride, int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages,
-                         int tokens, int heads, int kv_heads, int dk, int dv, int writes, int flags) {
+                         int tokens, int heads, int kv_heads, int dk, int dv, int writes, int flags,
+                         const float* __restrict__ v_first, int ld_first, const float* __restrict__ vmix) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
     __shared__ float x_s[FX_WARPS][FX_MAX_D];
@@ -55,12 +60,26 @@ attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ 
     }
     if (dst == nullptr) return;
     if (!is_q && !is_k) {
+        if (v_first != nullptr) {       // the blend with another layer's values of this token
+            const float lam = vmix[0];
+            const float* fr = v_first + (size_t)t * ld_first + (size_t)head * dv;
+            for (int c = lane; c < d; c += 32) Elem<T>::store(dst + c, (1.0f - lam) * src[c] + lam * fr[c]);
+            return;
+        }
         for (int c = lane; c < d; c += 32) Elem<T>::store(dst + c, src[c]);
         return;
     }
     const float* gain = is_q ? q_gain : k_gain;
     float norm = 1.0f;
-    if (gain != nullptr) {
+    if (gain != nullptr && (flags & FXP_NORM_WHOLE)) {
+        // one root mean square over all heads of the projection; every warp of the token sums the row in the same order
+        const int n_all = (is_q ? heads : kv_heads) * dk;
+        const float* all = qkv + (size_t)t * ld + (is_q ? 0 : (size_t)heads * dk);
+        float ss = 0.f;
+        for (int c = lane; c < n_all; c += 32) ss = fmaf(all[c], all[c], ss);
+        norm = 1.0f / sqrtf(warp_sum(ss) / (float)n_all + eps);
+        gain += (size_t)head * dk;
+    } else if (gain != nullptr) {
         float ss = 0.f;
         for (int c = lane; c < d; c += 32) ss = fmaf(src[c], src[c], ss);
         norm = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
@@ -101,23 +120,26 @@ attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ 
 NIB_API int nib_attention_prepare(const float* qkv, int ld, void* q_out, const float* q_gain, const float* k_gain, float eps,
                                   const float* freq, int rot, const int* positions, const int* req_index, const int* block_table,
                                   int bt_stride, int page_size, void* k_pages, void* v_pages, int num_pages, int tokens, int heads,
-                                  int kv_heads, int dk, int dv, int writes, int dtype, int flags, cudaStream_t stream) {
+                                  int kv_heads, int dk, int dv, int writes, int dtype, int flags, const float* v_first, int ld_first,
+                                  const float* vmix, cudaStream_t stream) {
     NIB_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0, "attention_prepare: bad head counts");
     NIB_REQUIRE(dk > 0 && dk <= FX_MAX_D && dv > 0 && dv <= FX_MAX_D, "attention_prepare: head sizes %d / %d are outside 1..%d", dk, dv, FX_MAX_D);
     NIB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dk && (rot == 0 || freq != nullptr), "attention_prepare: bad rotated width %d", rot);
     NIB_REQUIRE((q_gain == nullptr) == (k_gain == nullptr), "attention_prepare: q and k are normed together or not at all");
     NIB_REQUIRE(!(flags & FXP_VALUES_ARE_KEYS) || dk == dv, "attention_prepare: values that are the keys have the keys' width");
     NIB_REQUIRE(!writes || (page_size > 0 && num_pages > 0 && block_table != nullptr), "attention_prepare: bad pages");
+    NIB_REQUIRE(v_first == nullptr || (vmix != nullptr && ld_first >= kv_heads * dv && !(flags & FXP_VALUES_ARE_KEYS)),
+                "attention_prepare: a blend of values needs its factor and rows of at least kv_heads * dv floats");
     if (tokens == 0) return 0;
     const dim3 grid(ceil_div((long long)tokens * (heads + 2 * kv_heads), FX_WARPS)), block(FX_WARPS * 32);
     if (dtype == NIB_F32)
         NIB_CUDA(launch_pdl(attention_prepare_kernel<float>, grid, block, (size_t)0, stream, qkv, ld, (float*)q_out, q_gain, k_gain, eps, freq, rot,
                             positions, req_index, block_table, bt_stride, page_size, (float*)k_pages, (float*)v_pages, num_pages, tokens, heads,
-                            kv_heads, dk, dv, writes, flags));
+                            kv_heads, dk, dv, writes, flags, v_first, ld_first, vmix));
     else if (dtype == NIB_BF16)
         NIB_CUDA(launch_pdl(attention_prepare_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, qkv, ld, (__nv_bfloat16*)q_out, q_gain, k_gain,
                             eps, freq, rot, positions, req_index, block_table, bt_stride, page_size, (__nv_bfloat16*)k_pages,
-                            (__nv_bfloat16*)v_pages, num_pages, tokens, heads, kv_heads, dk, dv, writes, flags));
+                            (__nv_bfloat16*)v_pages, num_pages, tokens, heads, kv_heads, dk, dv, writes, flags, v_first, ld_first, vmix));
     else
         NIB_REQUIRE(false, "attention_prepare: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();
@@ -159,7 +181,7 @@ attention_flex_kernel(const T* __restrict__ q, int q_stride, TO* __restrict__ ou
                       const int* __restrict__ req_index, const int* __restrict__ block_table, int bt_stride, int page_size,
                       const T* __restrict__ k_pages, const T* __restrict__ v_pages, int num_pages, int m_tokens, int heads,
                       int kv_heads, int dk, int dv, float scale, float softcap, const float* __restrict__ slopes, int window,
-                      int chunk, float out_scale) {
+                      int chunk, float out_scale, const float* __restrict__ sinks) {
     __shared__ __align__(16) float q_s[FX_WARPS][FX_MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long w = (long long)blockIdx.x * FX_WARPS + warp;
@@ -216,7 +238,14 @@ attention_flex_kernel(const T* __restrict__ q, int q_stride, TO* __restrict__ ou
         m_run = m_new;
     }
     TO* o = out + (size_t)token * heads * dv + (size_t)head * dv;
-    const float inv = l_run > 0.f ? out_scale / l_run : 0.f;
+    float corr_sink = 1.0f;
+    if (sinks != nullptr) {     // one more term of the denominator, with no value
+        const float sk = sinks[head];
+        const float m_new = fmaxf(m_run, sk);
+        corr_sink = (m_run == -INFINITY) ? 0.f : expf(m_run - m_new);
+        l_run = l_run * corr_sink + expf(sk - m_new);
+    }
+    const float inv = l_run > 0.f ? out_scale * corr_sink / l_run : 0.f;
 #pragma unroll
     for (int i = 0; i < FX_MAX_D / 32; ++i) {
         const int d = lane + 32 * i;
@@ -229,7 +258,8 @@ attention_flex_kernel(const T* __restrict__ q, int q_stride, TO* __restrict__ ou
 NIB_API int nib_attention_flex(const void* q, int q_stride, void* out, int out_f32, const int* positions, const int* req_index,
                                const int* block_table, int bt_stride, int page_size, const void* k_pages, const void* v_pages,
                                int num_pages, int m_tokens, int heads, int kv_heads, int dk, int dv, float scale, float softcap,
-                               const float* slopes, int window, int chunk, float out_scale, int dtype, cudaStream_t stream) {
+                               const float* slopes, int window, int chunk, float out_scale, const float* sinks, int dtype,
+                               cudaStream_t stream) {
     NIB_REQUIRE(m_tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "attention: bad head counts %d / %d", heads, kv_heads);
     NIB_REQUIRE(dk > 0 && dk <= FX_MAX_D && dv > 0 && dv <= FX_MAX_D, "attention: head sizes %d / %d are outside 1..%d", dk, dv, FX_MAX_D);
     NIB_REQUIRE(page_size > 0 && num_pages > 0 && window >= 0 && chunk >= 0 && softcap >= 0.f, "attention: bad page_size/num_pages/window/chunk/cap");
@@ -238,7 +268,7 @@ NIB_API int nib_attention_flex(const void* q, int q_stride, void* out, int out_f
 #define NIB_FX_LAUNCH(T, TO)                                                                                                       \
     attention_flex_kernel<T, TO><<<blocks, FX_WARPS * 32, 0, stream>>>((const T*)q, q_stride, (TO*)out, positions, req_index, block_table, \
         bt_stride, page_size, (const T*)k_pages, (const T*)v_pages, num_pages, m_tokens, heads, kv_heads, dk, dv, scale, softcap, slopes,  \
-        window, chunk, out_scale)
+        window, chunk, out_scale, sinks)
     if (dtype == NIB_F32) NIB_FX_LAUNCH(float, float);
     else if (dtype == NIB_BF16 && out_f32) NIB_FX_LAUNCH(__nv_bfloat16, float);
     else if (dtype == NIB_BF16) NIB_FX_LAUNCH(__nv_bfloat16, __nv_bfloat16);

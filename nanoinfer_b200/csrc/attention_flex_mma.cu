@@ -8,7 +8,9 @@
 // products then add zeros). Scores leave the tensor cores as floats: scale, soft cap, distance bias and the masks
 // (causal, window, chunk; all by absolute position) are applied in 32-bit, then the online softmax of
 // attention_common.cuh. Key tiles start at absolute multiples of 64, so a position's result does not depend on what else
-// is in the batch; it depends on the cut only through which rows share a tile, i.e. by rounding.
+// is in the batch; it depends on the cut only through which rows share a tile, i.e. by rounding. With `sinks` the
+// denominator of a row of head h holds exp(sinks[h]) once more (no key, no value): it enters where a row is normalized,
+// here or, with split keys, in the merge.
 #include "attention_common.cuh"
 
 namespace {
@@ -100,7 +102,8 @@ attention_flex_mma_kernel(const __nv_bfloat16* __restrict__ q_in, int q_stride, 
                           const int* __restrict__ block_table, int bt_stride, int page_size,
                           const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages, int num_pages,
                           int heads, int kv_heads, int dk, int dv, float scale, float softcap, const float* __restrict__ slopes,
-                          int window, int chunk, float out_scale, int splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+                          int window, int chunk, float out_scale, int splits, float* __restrict__ part_o, float* __restrict__ part_ml,
+                          const float* __restrict__ sinks) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int req = blockIdx.y, kvh = blockIdx.z;
     const int n_rep = heads / kv_heads;
@@ -132,7 +135,7 @@ attention_flex_mma_kernel(const __nv_bfloat16* __restrict__ q_in, int q_stride, 
         return lo;
     };
     int vis_lo[2], vis_hi[2];
-    float slope2[2];
+    float slope2[2], sink2[2];
     const __nv_bfloat16* q_ptr[2];
     long long out_off[2];
 #pragma unroll
@@ -144,10 +147,11 @@ attention_flex_mma_kernel(const __nv_bfloat16* __restrict__ q_in, int q_stride, 
             vis_hi[r] = p;
             vis_lo[r] = first_visible(p);
             slope2[r] = slopes != nullptr ? slopes[head] * LOG2E : 0.f;
+            sink2[r] = sinks != nullptr ? sinks[head] * LOG2E : -INFINITY;
             q_ptr[r] = q_in + (size_t)(row_begin + ti) * q_stride + (size_t)head * dk;
             out_off[r] = ((long long)(row_begin + ti) * heads + head) * dv;
         } else {
-            vis_hi[r] = -1; vis_lo[r] = 0; slope2[r] = 0.f; q_ptr[r] = nullptr; out_off[r] = -1;
+            vis_hi[r] = -1; vis_lo[r] = 0; slope2[r] = 0.f; sink2[r] = -INFINITY; q_ptr[r] = nullptr; out_off[r] = -1;
         }
     }
     // key range of the whole CTA: the first visible key does not decrease with the position
@@ -249,7 +253,13 @@ attention_flex_mma_kernel(const __nv_bfloat16* __restrict__ q_in, int q_stride, 
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         if (out_off[r] < 0) continue;
-        const float inv = l_run[r] > 0.f ? out_scale / l_run[r] : 0.f;
+        float corr = 1.0f;
+        if (sink2[r] != -INFINITY) {        // the sink: one more term of the denominator (base-2 units like the maxima)
+            const float m_new = fmaxf(m_run[r], sink2[r]);
+            corr = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - m_new);
+            l_run[r] = l_run[r] * corr + exp2f(sink2[r] - m_new);
+        }
+        const float inv = l_run[r] > 0.f ? out_scale * corr / l_run[r] : 0.f;
         TO* orow = out + out_off[r];
 #pragma unroll
         for (int d = 0; d < DVP / 8; ++d)
@@ -261,12 +271,13 @@ attention_flex_mma_kernel(const __nv_bfloat16* __restrict__ q_in, int q_stride, 
 template <typename TO>
 __global__ void __launch_bounds__(128)
 attention_flex_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, TO* __restrict__ out, int splits, int dv,
-                            float out_scale) {
+                            float out_scale, const float* __restrict__ sinks, int heads) {
     pdl_wait();
-    const size_t row = blockIdx.x;
-    float m = -INFINITY;
+    const size_t row = blockIdx.x;      // token * heads + head
+    const float sink2 = sinks != nullptr ? sinks[row % heads] * LOG2E : -INFINITY;
+    float m = sink2;
     for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(row * splits + s) * 2]);
-    float l = 0.f;
+    float l = sink2 != -INFINITY ? exp2f(sink2 - m) : 0.f;
     for (int s = 0; s < splits; ++s) {
         const float ms = part_ml[(row * splits + s) * 2];
         if (ms != -INFINITY) l += part_ml[(row * splits + s) * 2 + 1] * exp2f(ms - m);
@@ -286,7 +297,7 @@ template <int DKP, int DVP, typename TO>
 int fx_launch(const void* q, int q_stride, void* out, const int* q_start, const int* ctx_lens, const int* block_table, int bt_stride,
               int page_size, const void* k_pages, const void* v_pages, int num_pages, int n_req, int max_q_len, int heads, int kv_heads,
               int dk, int dv, float scale, float softcap, const float* slopes, int window, int chunk, float out_scale, int splits,
-              float* part_o, float* part_ml, int m_tokens, cudaStream_t stream) {
+              float* part_o, float* part_ml, int m_tokens, const float* sinks, cudaStream_t stream) {
     static bool configured = false;
     const int smem = 2 * FxTile<DKP>::BYTES + 2 * FxTile<DVP>::BYTES;
     if (!configured) {
@@ -298,10 +309,10 @@ int fx_launch(const void* q, int q_stride, void* out, const int* q_start, const 
     NIB_CUDA(launch_pdl(attention_flex_mma_kernel<DKP, DVP, TO>, grid, dim3(FWARPS * 32), (size_t)smem, stream, (const __nv_bfloat16*)q, q_stride,
                         (TO*)out, q_start, ctx_lens, block_table, bt_stride, page_size, (const __nv_bfloat16*)k_pages,
                         (const __nv_bfloat16*)v_pages, num_pages, heads, kv_heads, dk, dv, scale, softcap, slopes, window, chunk, out_scale,
-                        splits, part_o, part_ml));
+                        splits, part_o, part_ml, sinks));
     if (splits > 1)
         NIB_CUDA(launch_pdl(attention_flex_merge_kernel<TO>, dim3(m_tokens * heads), dim3(128), (size_t)0, stream, (const float*)part_o,
-                            (const float*)part_ml, (TO*)out, splits, dv, out_scale));
+                            (const float*)part_ml, (TO*)out, splits, dv, out_scale, sinks, heads));
     return 0;
 }
 
@@ -320,7 +331,7 @@ NIB_API int nib_attention_flex_mma(const void* q, int q_stride, void* out, int o
                                    const int* block_table, int bt_stride, int page_size, const void* k_pages, const void* v_pages,
                                    int num_pages, int n_req, int max_q_len, int heads, int kv_heads, int dk, int dv, float scale,
                                    float softcap, const float* slopes, int window, int chunk, float out_scale, int splits, float* part_o,
-                                   float* part_ml, int m_tokens, cudaStream_t stream) {
+                                   float* part_ml, int m_tokens, const float* sinks, cudaStream_t stream) {
     NIB_REQUIRE(nib_attention_flex_mma_supported(heads, kv_heads, dk, dv, q_stride) == 1, "attention (tensor cores): head sizes %d / %d or head counts %d / %d are not taken", dk, dv, heads, kv_heads);
     NIB_REQUIRE(n_req >= 0 && max_q_len > 0 && page_size > 0 && num_pages > 0 && window >= 0 && chunk >= 0 && softcap >= 0.f, "attention (tensor cores): bad sizes");
     NIB_REQUIRE(splits <= 1 || (max_q_len * (heads / kv_heads) <= 64 && part_o != nullptr && part_ml != nullptr),
@@ -330,11 +341,11 @@ NIB_API int nib_attention_flex_mma(const void* q, int q_stride, void* out, int o
     do {                                                                                                                                    \
         const int rc = out_f32 ? fx_launch<DKP, DVP, float>(q, q_stride, out, q_start, ctx_lens, block_table, bt_stride, page_size, k_pages, \
                                                             v_pages, num_pages, n_req, max_q_len, heads, kv_heads, dk, dv, scale, softcap,   \
-                                                            slopes, window, chunk, out_scale, splits, part_o, part_ml, m_tokens, stream)      \
+                                                            slopes, window, chunk, out_scale, splits, part_o, part_ml, m_tokens, sinks, stream) \
                                    : fx_launch<DKP, DVP, __nv_bfloat16>(q, q_stride, out, q_start, ctx_lens, block_table, bt_stride,         \
                                                                         page_size, k_pages, v_pages, num_pages, n_req, max_q_len, heads,     \
                                                                         kv_heads, dk, dv, scale, softcap, slopes, window, chunk, out_scale,  \
-                                                                        splits, part_o, part_ml, m_tokens, stream);                          \
+                                                                        splits, part_o, part_ml, m_tokens, sinks, stream);                   \
         if (rc != 0) return rc;                                                                                                             \
     } while (0)
     if (dk <= 64 && dv <= 64) NIB_FXM(64, 64);

@@ -670,9 +670,11 @@ class Kernels:
         for b in range(nb):
             self.linear(a_blocks[b], w_blocks[b], None if bias32 is None else bias32[b], out32[b], "f32")
 
-    def rmsnorm_add(self, y32, gain32, eps, mult, x32, h_out=None, clear=False):
+    def rmsnorm_add(self, y32, gain32, eps, mult, x32, h_out=None, clear=False, next_gain32=None, next_eps=0.0):
         """x32 += mult * y32 / rms(y32) * gain32, row by row (``eps`` inside the root): the residual sum of a block whose norm
-        stands on a sublayer's output. ``h_out``: the new x32 also in that tensor's type. ``clear``: y32 is left zeroed."""
+        stands on a sublayer's output. ``h_out``: the new x32 also in that tensor's type. ``clear``: y32 is left zeroed.
+        With ``next_gain32`` what goes to ``h_out`` is the next sublayer's norm of the new row instead:
+        x32 / rms(x32) * next_gain32 with ``next_eps``."""
         self._rows(y32, torch.float32, "rmsnorm_add y"); self._rows(x32, torch.float32, "rmsnorm_add x"); _need(gain32, torch.float32, "rmsnorm_add gain")
         m, n = x32.shape
         if tuple(y32.shape) != (m, n) or gain32.numel() != n or not y32.is_contiguous() or not x32.is_contiguous():
@@ -681,26 +683,36 @@ class Kernels:
             _need(h_out, None, "rmsnorm_add h")
             if tuple(h_out.shape) != (m, n):
                 raise KernelError("rmsnorm_add: h_out has the stream's shape")
+        if next_gain32 is not None:
+            _need(next_gain32, torch.float32, "rmsnorm_add next gain")
+            if next_gain32.numel() != n or h_out is None:
+                raise KernelError("rmsnorm_add: the next norm has a gain of the row's size and a tensor to go to")
         self._check(self._lib.nib_rmsnorm_add(_ptr(y32), _ptr(gain32), _ptr(x32), _ptr(h_out), c_int(m), c_int(n), c_float(eps), c_float(mult),
-                                              c_int(1 if clear else 0), c_int(_DT[h_out.dtype] if h_out is not None else 0), self._stream()),
-                    "rmsnorm_add")
+                                              c_int(1 if clear else 0), c_int(_DT[h_out.dtype] if h_out is not None else 0), _ptr(next_gain32),
+                                              c_float(next_eps), self._stream()), "rmsnorm_add")
 
     # ---- routed experts (moe.cu) ---------------------------------------------------------------------------
-    def moe_route(self, z32, top, sel_e, sel_w):
+    def moe_route(self, z32, top, sel_e, sel_w, score="sigmoid", renormalize=False, correction32=None):
         """From the router logits z32 [tokens, experts]: sel_e [tokens, top] int32 = the experts with the largest logits (the
-        first of equal ones), sel_w [tokens, top] = sigmoid of their logits."""
+        first of equal ones), sel_w [tokens, top] = sigmoid of their logits. Options: ``score`` 'softmax' (over all the logits
+        of a token); ``correction32`` [experts] is added to the scores for the choice alone; ``renormalize`` divides the chosen
+        scores by their sum + 1e-20. With an option z32 is overwritten by the scores."""
         self._rows(z32, torch.float32, "moe_route z"); _need(sel_e, torch.int32, "moe_route experts"); _need(sel_w, torch.float32, "moe_route weights")
         m, experts = z32.shape
         if tuple(sel_e.shape) != (m, top) or tuple(sel_w.shape) != (m, top):
             raise KernelError("moe_route: shapes do not fit")
+        if correction32 is not None:
+            _need(correction32, torch.float32, "moe_route correction")
+            if correction32.numel() != experts:
+                raise KernelError("moe_route: one correction per router output")
         self._check(self._lib.nib_moe_route(_ptr(z32), c_int(z32.stride(0)), _ptr(sel_e), _ptr(sel_w), c_int(m), c_int(experts), c_int(top),
-                                            self._stream()), "moe_route")
+                                            c_int(_moe_mode(score, renormalize)), _ptr(correction32), self._stream()), "moe_route")
 
     def _moe_tc(self, h, w_gate_up, w_down) -> bool:
         """bfloat16 in widths of 8 takes the tensor-core products; everything else (32-bit, odd widths) the CUDA cores."""
-        experts, ff2, hidden = w_gate_up.shape
+        experts, _, hidden = w_gate_up.shape
         return h.dtype == torch.bfloat16 and not self.options.force_simt_gemm and self._lib.nib_moe_tc_supported(
-            _ptr(h), c_int(h.stride(0)), _ptr(w_gate_up), _ptr(w_down), c_int(experts), c_int(hidden), c_int(ff2 // 2)) == 1
+            _ptr(h), c_int(h.stride(0)), _ptr(w_gate_up), _ptr(w_down), c_int(experts), c_int(hidden), c_int(w_down.shape[2])) == 1
 
     def _moe_tables(self, n, experts, tc, dev):
         """Row tiles of 128 for the tensor cores (of 32 while an expert gets few rows: a decode step), of 64 for the CUDA
@@ -711,73 +723,122 @@ class Kernels:
         return SimpleNamespace(tile_rows=tile_rows, max_tiles=max_tiles, row_of=idx[:n], src_of=idx[n:2 * n],
                                tiles=idx[2 * n:2 * n + 3 * max_tiles], n_tiles=idx[2 * n + 3 * max_tiles:], rows=None)
 
-    def moe_step(self, h, w_router, top, w_gate_up, w_down, sel_e, sel_w):
+    def moe_step(self, h, w_router, top, w_gate_up, w_down, sel_e, sel_w, score="sigmoid", renormalize=False, correction32=None,
+                 n_real=None, extra=0, z_extra=None):
         """A step of few tokens: router logits (32-bit sums over the stored ``h``), the choice, the grouping and the rows
-        in the experts' order in ONE launch. Fills sel_e and sel_w like ``moe_route`` and returns what ``moe_experts``
-        takes as ``plan``; None when the step is too large for one block (the caller then takes the separate steps)."""
+        in the experts' order in ONE launch. Fills sel_e and sel_w like ``moe_route`` (same options) and returns what
+        ``moe_experts`` takes as ``plan``; None when the step is too large for one block (the caller then takes the separate
+        steps). ``n_real``: the first so many router outputs are experts (the others get no rows to multiply). ``extra``: the
+        last so many rows of ``w_router`` are no router outputs; their logits go to ``z_extra`` [tokens, extra]."""
         _need(h, None, "moe_step h"); _need(w_router, h.dtype, "moe_step router")
         m, hidden = h.shape
-        experts = w_router.shape[0]
-        if m == 0 or self.options.no_moe_step or self._lib.nib_moe_step_supported(c_int(m), c_int(hidden), c_int(experts), c_int(top)) != 1:
+        experts = w_router.shape[0] - extra
+        n_real = experts if n_real is None else n_real
+        if m == 0 or self.options.no_moe_step or top > experts or \
+                self._lib.nib_moe_step_supported(c_int(m), c_int(hidden), c_int(experts + extra), c_int(top)) != 1:
             return None
+        if extra:
+            _need(z_extra, torch.float32, "moe_step extra logits")
+            if tuple(z_extra.shape) != (m, extra):
+                raise KernelError("moe_step: the extra logits are [tokens, extra]")
+        if correction32 is not None:
+            _need(correction32, torch.float32, "moe_step correction")
+            if correction32.numel() != experts:
+                raise KernelError("moe_step: one correction per router output")
         tc = self._moe_tc(h, w_gate_up, w_down)
         plan = self._moe_tables(m * top, experts, tc, h.device)
         if tc:
             plan.rows = torch.empty((m * top, hidden), dtype=h.dtype, device=h.device)
         self._check(self._lib.nib_moe_step(_ptr(h), c_int(h.stride(0)), _ptr(w_router), c_int(m), c_int(hidden), c_int(experts), c_int(top),
                                            _ptr(sel_e), _ptr(sel_w), c_int(plan.tile_rows), _ptr(plan.row_of), _ptr(plan.src_of), _ptr(plan.tiles),
-                                           _ptr(plan.n_tiles), c_int(plan.max_tiles), _ptr(plan.rows), c_int(_DT[h.dtype]), self._stream()),
-                    "experts: router, choice and grouping of a short step")
+                                           _ptr(plan.n_tiles), c_int(plan.max_tiles), _ptr(plan.rows), c_int(_DT[h.dtype]),
+                                           c_int(_moe_mode(score, renormalize)), _ptr(correction32), c_int(n_real), c_int(extra), _ptr(z_extra),
+                                           self._stream()), "experts: router, choice and grouping of a short step")
         return plan
 
-    def moe_experts(self, h, sel_e, sel_w, w_gate_up, w_down, out32, plan=None):
+    def moe_experts(self, h, sel_e, sel_w, w_gate_up, w_down, out32, plan=None, gated=True, weight_on="input", outputs=None):
         """out32[t] += sum over the token's choices c of W_down,e (silu(W_gate,e x) * (W_up,e x)) with e = sel_e[t, c] and
         x = sel_w[t, c] * h[t]: the weight stands on the expert's input. w_gate_up [experts, 2 ff, hidden] (gate rows, then up
-        rows), w_down [experts, hidden, ff]. ``plan``: what ``moe_step`` returned for these choices.
+        rows), w_down [experts, hidden, ff]. ``plan``: what ``moe_step`` returned for these choices. Options: ``gated`` False:
+        experts W_down relu(W_up x)^2 with w_gate_up [experts, ff, hidden]; ``weight_on`` 'output': x = h[t] and the weight
+        multiplies the expert's result; ``outputs``: how many outputs the router has when some of them (from ``experts`` on)
+        are no experts: choices of those add nothing here.
 
         On the CUDA cores a token's choices are summed in ascending order; on the tensor cores they are added into the
         token's row by reductions in memory, in no fixed order."""
         _need(h, None, "moe_experts h"); _need(w_gate_up, h.dtype, "moe_experts w_gate_up"); _need(w_down, h.dtype, "moe_experts w_down")
         _need(sel_e, torch.int32, "moe_experts experts"); _need(sel_w, torch.float32, "moe_experts weights"); _need(out32, torch.float32, "moe_experts out")
         m, hidden = h.shape
-        experts, ff2, _ = w_gate_up.shape
-        ff, top = ff2 // 2, sel_e.shape[1]
-        if tuple(w_gate_up.shape) != (experts, 2 * ff, hidden) or tuple(w_down.shape) != (experts, hidden, ff) or tuple(out32.shape) != (m, hidden) \
-                or tuple(sel_e.shape) != (m, top) or tuple(sel_w.shape) != (m, top):
+        experts, top, ff = w_gate_up.shape[0], sel_e.shape[1], w_down.shape[2]
+        if tuple(w_gate_up.shape) != (experts, (2 if gated else 1) * ff, hidden) or tuple(w_down.shape) != (experts, hidden, ff) \
+                or tuple(out32.shape) != (m, hidden) or tuple(sel_e.shape) != (m, top) or tuple(sel_w.shape) != (m, top):
             raise KernelError("moe_experts: shapes do not fit")
+        if weight_on not in ("input", "output"):
+            raise KernelError(f"moe_experts: the weight stands on the input or the output, not '{weight_on}'")
         if m == 0:
             return
         n, dev, dt = m * top, h.device, c_int(_DT[h.dtype])
+        first, w_out = c_int(1 if gated else 2), c_int(1 if weight_on == "output" else 0)
+        outputs = experts if outputs is None else outputs
         tc = self._moe_tc(h, w_gate_up, w_down)
         p = plan
         if p is None:
-            p = self._moe_tables(n, experts, tc, dev)
-            self._check(self._lib.nib_moe_group(_ptr(sel_e), c_int(n), c_int(experts), c_int(p.tile_rows), _ptr(p.row_of), _ptr(p.src_of), _ptr(p.tiles),
-                                                _ptr(p.n_tiles), c_int(p.max_tiles), self._stream()), "moe_group")
+            p = self._moe_tables(n, outputs, tc, dev)
+            self._check(self._lib.nib_moe_group(_ptr(sel_e), c_int(n), c_int(outputs), c_int(p.tile_rows), _ptr(p.row_of), _ptr(p.src_of), _ptr(p.tiles),
+                                                _ptr(p.n_tiles), c_int(p.max_tiles), c_int(experts), self._stream()), "moe_group")
         act = torch.empty((n, ff), dtype=h.dtype, device=dev)
         if tc:
             if p.rows is None:
                 p.rows = torch.empty((n, hidden), dtype=h.dtype, device=dev)
                 self._check(self._lib.nib_moe_gather_rows(_ptr(h), c_int(h.stride(0)), _ptr(p.rows), c_int(hidden), _ptr(p.src_of), c_int(n), c_int(hidden),
                                                           c_int(top), self._stream()), "experts: rows in the experts' order")
-            self._check(self._lib.nib_moe_gemm_tc(c_int(1), _ptr(p.rows), c_int(hidden), c_int(n), _ptr(w_gate_up), c_int(experts), _ptr(act), c_int(ff),
+            self._check(self._lib.nib_moe_gemm_tc(first, _ptr(p.rows), c_int(hidden), c_int(n), _ptr(w_gate_up), c_int(experts), _ptr(act), c_int(ff),
                                                   _ptr(p.tiles), _ptr(p.n_tiles), c_int(p.max_tiles), _ptr(p.src_of), _ptr(sel_w), c_int(top), c_int(ff),
-                                                  c_int(hidden), c_int(0), c_int(p.tile_rows), self._stream()), "experts: gate, up, activation (tensor cores)")
+                                                  c_int(hidden), c_int(0), c_int(p.tile_rows), w_out, self._stream()), "experts: gate, up, activation (tensor cores)")
             self._check(self._lib.nib_moe_gemm_tc(c_int(0), _ptr(act), c_int(ff), c_int(n), _ptr(w_down), c_int(experts), _ptr(out32), c_int(out32.stride(0)),
                                                   _ptr(p.tiles), _ptr(p.n_tiles), c_int(p.max_tiles), _ptr(p.src_of), _ptr(sel_w), c_int(top), c_int(hidden),
-                                                  c_int(ff), c_int(1 if top == 1 else 2), c_int(p.tile_rows), self._stream()), "experts: down (tensor cores)")
+                                                  c_int(ff), c_int(1 if top == 1 else 2), c_int(p.tile_rows), w_out, self._stream()), "experts: down (tensor cores)")
             return
         scatter = top == 1      # one choice per token: its result goes straight into the token's row
-        y = out32 if scatter else torch.empty((n, hidden), dtype=torch.float32, device=dev)
-        self._check(self._lib.nib_moe_gemm_simt(c_int(1), _ptr(h), c_int(h.stride(0)), _ptr(w_gate_up), _ptr(act), c_int(ff), _ptr(p.tiles), _ptr(p.n_tiles),
+        # (rows of choices that are no experts belong to no tile: they must read as zeros in the sum of a token's choices)
+        y = out32 if scatter else (torch.empty if outputs == experts else torch.zeros)((n, hidden), dtype=torch.float32, device=dev)
+        self._check(self._lib.nib_moe_gemm_simt(first, _ptr(h), c_int(h.stride(0)), _ptr(w_gate_up), _ptr(act), c_int(ff), _ptr(p.tiles), _ptr(p.n_tiles),
                                                 c_int(p.max_tiles), _ptr(p.src_of), _ptr(sel_w), c_int(top), c_int(ff), c_int(hidden), c_int(0), dt,
-                                                self._stream()), "experts: gate, up, activation")
+                                                w_out, self._stream()), "experts: gate, up, activation")
         self._check(self._lib.nib_moe_gemm_simt(c_int(0), _ptr(act), c_int(ff), _ptr(w_down), _ptr(y), c_int(y.stride(0)), _ptr(p.tiles), _ptr(p.n_tiles),
                                                 c_int(p.max_tiles), _ptr(p.src_of), _ptr(sel_w), c_int(top), c_int(hidden), c_int(ff), c_int(1 if scatter else 0),
-                                                dt, self._stream()), "experts: down")
+                                                dt, w_out, self._stream()), "experts: down")
         if not scatter:
             self._check(self._lib.nib_moe_combine(_ptr(y), _ptr(p.row_of), _ptr(out32), c_int(m), c_int(hidden), c_int(top), self._stream()),
                         "experts: sum of a token's choices")
+
+    def moe_side(self, h, out32=None, sel_e=None, sel_w=None, n_real=0, u32=None, act=None, gate32=None, kind="relu2"):
+        """What stands beside routed experts, per token, in one launch; either half may be absent. Identity experts (with
+        ``sel_e``): out32[t] += (the sum of sel_w[t, c] over the choices with sel_e[t, c] >= n_real) * h[t]. The activation of
+        an expert that every token uses (with ``act``): act[t] = g * f(u32[t]) in h's type, f = relu(.)^2 (``kind`` 'relu2')
+        or the identity ('none'), g = sigmoid(gate32[t]) with one gate logit per token (a column, any row stride), else 1."""
+        _need(h, None, "moe_side h")
+        m, hidden = h.shape
+        top = ff = 0
+        if sel_e is not None:
+            _need(sel_e, torch.int32, "moe_side experts"); _need(sel_w, torch.float32, "moe_side weights"); self._rows(out32, torch.float32, "moe_side out")
+            top = sel_e.shape[1]
+            if tuple(sel_e.shape) != (m, top) or tuple(sel_w.shape) != (m, top) or tuple(out32.shape) != (m, hidden):
+                raise KernelError("moe_side: shapes do not fit")
+        if act is not None:
+            self._rows(u32, torch.float32, "moe_side u"); self._rows(act, h.dtype, "moe_side act")
+            ff = u32.shape[1]
+            if tuple(u32.shape) != (m, ff) or tuple(act.shape) != (m, ff):
+                raise KernelError("moe_side: shapes do not fit")
+            if gate32 is not None:
+                _need(gate32, torch.float32, "moe_side gate", contiguous=False)
+                if gate32.shape[0] != m or gate32.numel() != m:
+                    raise KernelError("moe_side: one gate logit per token")
+        self._check(self._lib.nib_moe_side(
+            _ptr(h), c_int(h.stride(0)), _ptr(sel_e), _ptr(sel_w), c_int(top), c_int(n_real), _ptr(out32), c_int(out32.stride(0) if out32 is not None else 0),
+            c_int(hidden), _ptr(u32), c_int(u32.stride(0) if u32 is not None else 0), _ptr(gate32), c_int(gate32.stride(0) if gate32 is not None else 0),
+            _ptr(act), c_int(act.stride(0) if act is not None else 0), c_int(ff), c_int({"none": 0, "relu2": 1}[kind]), c_int(m), c_int(_DT[h.dtype]),
+            self._stream()), "moe_side")
 
     # ---- gate, norm in groups, skip (pointwise.cu) ---------------------------------------------------------
     def gated_norm(self, o32, out, groups=0, eps=0.0, gain32=None, gate32=None, gate_kind="none", gate_first=False,
@@ -953,23 +1014,32 @@ class Kernels:
     # ---- attention with options (attention_flex.cu) --------------------------------------------------------
     def attention_prepare(self, qkv32, q_out, heads, kv_heads, dim, vdim, q_gain32, k_gain32, eps, freq32, rot_dims, ctx,
                           block_table, page_size, k_pages, v_pages, writes, layout="half", unit_norm_after=False,
-                          values_are_keys=False):
+                          values_are_keys=False, norm_whole=False, v_first32=None, vmix32=None):
         """From the 32-bit rows [q | k | v]: optional per-head RMS norm of q and k (gains of ``dim``), rotation of the first
         ``rot_dims`` elements of every q and k head by position * freq32 (``layout`` 'half': element i with i + rot_dims/2;
         'interleaved': 2i with 2i + 1), with ``unit_norm_after`` every q and k head divided by its root mean square after
         the rotation (no gain), queries into ``q_out`` in the storage type, and with ``writes`` keys and values into their
-        pages. With ``values_are_keys`` the rows are [q | k] and a value head is the key head as projected."""
+        pages. With ``values_are_keys`` the rows are [q | k] and a value head is the key head as projected. With
+        ``norm_whole`` the gains have the size of the whole projection (heads * dim, kv_heads * dim) and the root mean square
+        is taken over all of a token's q (and k) at once. With ``v_first32`` [tokens, kv_heads * vdim] (32-bit rows of any
+        stride) a value is written as (1 - vmix32[0]) v + vmix32[0] v_first32."""
         self._rows(qkv32, torch.float32, "attention_prepare qkv"); _need(q_out, None, "attention_prepare q")
         m = qkv32.shape[0]
         if qkv32.shape[1] != (heads + kv_heads) * dim + (0 if values_are_keys else kv_heads * vdim) or tuple(q_out.shape) != (m, heads * dim) \
                 or (values_are_keys and vdim != dim):
             raise KernelError("attention_prepare: widths do not fit the head counts")
-        flags = {"half": 0, "interleaved": 1}[layout] | (2 if unit_norm_after else 0) | (4 if values_are_keys else 0)
-        for t in (q_gain32, k_gain32):
+        flags = {"half": 0, "interleaved": 1}[layout] | (2 if unit_norm_after else 0) | (4 if values_are_keys else 0) | (8 if norm_whole else 0)
+        for t, n_heads in ((q_gain32, heads), (k_gain32, kv_heads)):
             if t is not None:
                 _need(t, torch.float32, "attention_prepare gain")
-                if t.numel() != dim:
-                    raise KernelError("attention_prepare: a gain has the size of a head")
+                if t.numel() != (n_heads * dim if norm_whole else dim):
+                    raise KernelError("attention_prepare: a gain has the size of a head (of the whole projection with norm_whole)")
+        ld_first = 0
+        if v_first32 is not None:
+            self._rows(v_first32, torch.float32, "attention_prepare v_first"); _need(vmix32, torch.float32, "attention_prepare vmix")
+            if tuple(v_first32.shape) != (m, kv_heads * vdim) or vmix32.numel() != 1 or values_are_keys:
+                raise KernelError("attention_prepare: the values to blend with are [tokens, kv_heads * vdim], the factor one number")
+            ld_first = v_first32.stride(0)
         if rot_dims:
             _need(freq32, torch.float32, "attention_prepare freq")
             if freq32.numel() != rot_dims // 2:
@@ -986,14 +1056,16 @@ class Kernels:
             _ptr(qkv32), c_int(qkv32.stride(0)), _ptr(q_out), _ptr(q_gain32), _ptr(k_gain32), c_float(eps), _ptr(freq32 if rot_dims else None),
             c_int(rot_dims), _ptr(ctx.positions), _ptr(ctx.req_index), _ptr(block_table if writes else None), c_int(bt_stride), c_int(page_size),
             _ptr(k_pages if writes else None), _ptr(v_pages if writes else None), c_int(num_pages), c_int(m), c_int(heads), c_int(kv_heads),
-            c_int(dim), c_int(vdim), c_int(1 if writes else 0), c_int(_DT[q_out.dtype]), c_int(flags), self._stream()), "attention_prepare")
+            c_int(dim), c_int(vdim), c_int(1 if writes else 0), c_int(_DT[q_out.dtype]), c_int(flags), _ptr(v_first32), c_int(ld_first),
+            _ptr(vmix32 if v_first32 is not None else None), self._stream()), "attention_prepare")
 
     def attention_flex(self, q, out, heads, kv_heads, dim, vdim, scale, softcap, slopes32, window, chunk, out_scale, ctx,
-                       block_table, page_size, k_pages, v_pages):
+                       block_table, page_size, k_pages, v_pages, sinks32=None):
         """Softmax attention of every token of the step over its request's cached keys: j <= own position, within
         ``window`` (0 = none) and within the own block of ``chunk`` positions (0 = none); score = (q . k) * scale, capped
         by ``softcap`` * tanh(. / softcap) (0 = none), minus slopes32[head] * distance (None = none). ``out``
-        [tokens, heads * vdim] in float or the storage type, times ``out_scale``."""
+        [tokens, heads * vdim] in float or the storage type, times ``out_scale``. With ``sinks32`` [heads] the softmax's
+        denominator holds exp(sinks32[head]) once more (no key, no value, neither scaled nor capped)."""
         _need(q, None, "attention q"); _need(out, None, "attention out")
         _need(k_pages, q.dtype, "k_pages"); _need(v_pages, q.dtype, "v_pages"); _need(block_table, torch.int32, "block_table", contiguous=False)
         m = q.shape[0]
@@ -1006,6 +1078,10 @@ class Kernels:
             _need(slopes32, torch.float32, "attention slopes")
             if slopes32.numel() != heads:
                 raise KernelError("attention_flex: one slope per head")
+        if sinks32 is not None:
+            _need(sinks32, torch.float32, "attention sinks")
+            if sinks32.numel() != heads:
+                raise KernelError("attention_flex: one sink per head")
         if q.dtype == torch.bfloat16 and not self.options.force_general_attention and page_size > 0 \
                 and self._lib.nib_attention_flex_mma_supported(c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(q.stride(0))) == 1:
             # bfloat16 heads of up to 128 (multiples of 8): tensor cores, prompt portions and decoded tokens alike
@@ -1027,13 +1103,13 @@ class Kernels:
                 _ptr(block_table), c_int(block_table.stride(0)), c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(k_pages.shape[0]),
                 c_int(ctx.host.num_requests), c_int(max(ctx.host.q_lens)), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_float(scale),
                 c_float(softcap), _ptr(slopes32), c_int(window), c_int(chunk), c_float(out_scale), c_int(splits), _ptr(part_o), _ptr(part_ml),
-                c_int(m), self._stream()), "attention (options, tensor cores)")
+                c_int(m), _ptr(sinks32), self._stream()), "attention (options, tensor cores)")
             return
         self._check(self._lib.nib_attention_flex(
             _ptr(q), c_int(q.stride(0)), _ptr(out), c_int(1 if out.dtype == torch.float32 else 0), _ptr(ctx.positions), _ptr(ctx.req_index),
             _ptr(block_table), c_int(block_table.stride(0)), c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(k_pages.shape[0]), c_int(m),
             c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_float(scale), c_float(softcap), _ptr(slopes32), c_int(window), c_int(chunk),
-            c_float(out_scale), c_int(_DT[q.dtype]), self._stream()), "attention (options)")
+            c_float(out_scale), _ptr(sinks32), c_int(_DT[q.dtype]), self._stream()), "attention (options)")
 
     # ---- recurrent mixers (recurrent.cu) -------------------------------------------------------------
     def delta_rule_scan(self, r32, k32, v32, a_logit32, w_logit32, state, ctx, o32, heads, d):
@@ -1249,6 +1325,13 @@ class Kernels:
 TIMELINE_KERNELS = {1: "embed", 2: "rmsnorm", 3: "rope_store", 4: "gemm_smallm", 5: "gemm_stream", 6: "gemm_tc",
                     7: "attention_decode", 8: "attention_combine", 9: "argmax", 10: "attention_decode_mma",
                     11: "gemm_pair", 12: "attention_prefill"}
+
+
+def _moe_mode(score: str, renormalize: bool) -> int:
+    """The router's options as the kernels' flag word."""
+    if score not in ("sigmoid", "softmax"):
+        raise KernelError(f"experts: scores are 'sigmoid' or 'softmax', not '{score}'")
+    return (1 if score == "softmax" else 0) | (2 if renormalize else 0)
 
 
 def _cluster_splits(n: int) -> int:

@@ -8,6 +8,9 @@
 //             token, else by reductions in memory (the order of a token's choices, and with it the last bit of a sum of
 //             three or more, is not fixed; two addends onto zeros give the same sum in either order).
 //
+// Experts without a gate (mode 2): act[row] = relu(w u)^2 from one accumulator. With `w_out` the score multiplies the
+// down product's result (in 32-bit, in its epilogue) instead of the first product's accumulators.
+//
 // A work item is (row tile of the table that moe_group wrote, tile of 128 output features). The table's length depends on
 // the routing and lives on the device: the grid is as large as the sizes allow (one CTA per SM at most) and every CTA reads
 // the count when it starts, so the launch never depends on the batch's content. A row tile never spans two experts, and
@@ -55,12 +58,14 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const unsigned*>(&v);
 }
 
-template <int TOK, bool GATE_UP>
+template <int TOK, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, void* __restrict__ out, int ldo,
               const int* __restrict__ tiles, const int* __restrict__ n_tiles, int max_tiles, const int* __restrict__ src_of,
-              const float* __restrict__ sel_w, int top, int n_out, int k_dim, int w_rows, int scatter, int splits, int kb_per_split) {
+              const float* __restrict__ sel_w, int top, int n_out, int k_dim, int w_rows, int scatter, int splits, int kb_per_split, int w_out) {
+    constexpr bool GATE_UP = MODE == 1, FIRST = MODE != 0;     // FIRST: the product that reads the tokens' rows and writes activations
     constexpr bool DUAL = GATE_UP;
+    const bool use_w = FIRST != (w_out != 0);                  // whether this product is the one the score multiplies
     // Row tiles of 128: the operands change places, so the ROWS are the instruction's M side (the TMEM lanes) and the 128
     // features its columns; a thread of the epilogue then owns a row and writes 16 consecutive features at a time.
     constexpr bool SWAP = (TOK == BLOCK_F);
@@ -196,8 +201,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                 size_t orow = 0;
                 if (live) {
                     const int entry = __ldg(src_of + row0 + t);
-                    wg = __ldg(sel_w + entry);
-                    orow = (size_t)((!GATE_UP && scatter) ? entry / top : row0 + t) * ldo;
+                    wg = use_w ? __ldg(sel_w + entry) : 1.0f;
+                    orow = (size_t)((!FIRST && scatter) ? entry / top : row0 + t) * ldo;
                 }
                 bool ok = !s_failed && mbar_wait(&acc_full_bar[buf], (local >> 1) & 1);
                 ok = __all_sync(0xffffffffu, ok);
@@ -221,13 +226,16 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                         if (GATE_UP) {
                             const float g = __uint_as_float(rv[j]) * wg, up = __uint_as_float(ru[j]) * wg;
                             x[j] = __fdividef(g, 1.0f + __expf(-g)) * up;      // the dense gated product's epilogue has the same forms
+                        } else if (FIRST) {
+                            const float u = fmaxf(__uint_as_float(rv[j]) * wg, 0.f);
+                            x[j] = u * u;
                         } else {
-                            x[j] = __uint_as_float(rv[j]);
+                            x[j] = __uint_as_float(rv[j]) * wg;
                         }
                     }
                     const int f = f0 + c;
                     const bool whole = f + 16 <= n_out;       // 16 features: 32 bytes of bfloat16 or 64 of floats, aligned
-                    if (GATE_UP) {
+                    if (FIRST) {
                         __nv_bfloat16* o = (__nv_bfloat16*)out + orow + f;
                         if (whole) {
                             uint4 p0, p1;
@@ -274,8 +282,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                 int orow = -1;
                 if (c < rows) {
                     const int entry = __ldg(src_of + row0 + c);
-                    wg = __ldg(sel_w + entry);
-                    orow = (!GATE_UP && scatter) ? entry / top : row0 + c;
+                    wg = use_w ? __ldg(sel_w + entry) : 1.0f;
+                    orow = (!FIRST && scatter) ? entry / top : row0 + c;
                 }
                 s_wgt[quad][c] = wg;
                 s_row[quad][c] = orow;
@@ -299,16 +307,19 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     for (int j = 0; j < 16; ++j) {
                         if (c + j >= rows) break;
                         const size_t o = (size_t)s_row[quad][c + j] * ldo + f;
+                        const float wg = s_wgt[quad][c + j];
                         if (GATE_UP) {
-                            const float wg = s_wgt[quad][c + j];
                             const float g = v[j] * wg, up = u[j] * wg;
                             ((__nv_bfloat16*)out)[o] = __float2bfloat16(__fdividef(g, 1.0f + __expf(-g)) * up);
+                        } else if (FIRST) {
+                            const float r = fmaxf(v[j] * wg, 0.f);
+                            ((__nv_bfloat16*)out)[o] = __float2bfloat16(r * r);
                         } else if (reduce) {
-                            atomicAdd((float*)out + o, v[j]);   // a token's choices, or the splits of K, meet in its row in no fixed order
+                            atomicAdd((float*)out + o, v[j] * wg);   // a token's choices, or the splits of K, meet in its row in no fixed order
                         } else if (scatter) {
-                            ((float*)out)[o] += v[j];       // one choice per token: nobody else writes this row
+                            ((float*)out)[o] += v[j] * wg;       // one choice per token: nobody else writes this row
                         } else {
-                            ((float*)out)[o] = v[j];
+                            ((float*)out)[o] = v[j] * wg;
                         }
                     }
                 }
@@ -378,24 +389,26 @@ int sm_count() {
     return sms;
 }
 
-template <int TOK, bool GATE_UP>
+template <int TOK, int MODE>
 int launch_moe_tc(const CUtensorMap& mw, const CUtensorMap& ma, void* out, int ldo, const int* tiles, const int* n_tiles, int max_tiles,
-                  const int* src_of, const float* sel_w, int top, int N, int K, int w_rows, int scatter, int splits, cudaStream_t stream) {
-    using C = Cfg<TOK, GATE_UP>;
+                  const int* src_of, const float* sel_w, int top, int N, int K, int w_rows, int scatter, int splits, int w_out,
+                  cudaStream_t stream) {
+    constexpr bool FIRST = MODE != 0;       // the first product, gated or not: its output cannot be split along K
+    using C = Cfg<TOK, MODE == 1>;
     static bool configured = false;
     if (!configured) {
-        NIB_CUDA(cudaFuncSetAttribute(moe_tc_kernel<TOK, GATE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        NIB_CUDA(cudaFuncSetAttribute(moe_tc_kernel<TOK, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         configured = true;
     }
     const int k_blocks = ceil_div(K, BLOCK_K);
-    if (splits < 1 || GATE_UP || scatter == 0) splits = 1;      // only sums into the output can be split along K
+    if (splits < 1 || FIRST || scatter == 0) splits = 1;      // only sums into the output can be split along K
     if (splits > k_blocks) splits = k_blocks;
     const int kb_per_split = ceil_div(k_blocks, splits);
     splits = ceil_div(k_blocks, kb_per_split);               // no split without work
     const long long most = (long long)max_tiles * ceil_div(N, BLOCK_F) * splits;
     const int sms = sm_count();
-    NIB_CUDA(launch_pdl(moe_tc_kernel<TOK, GATE_UP>, dim3((unsigned)(most < sms ? most : sms)), dim3(THREADS), (size_t)C::SMEM, stream, mw, ma, out, ldo,
-                        tiles, n_tiles, max_tiles, src_of, sel_w, top, N, K, w_rows, scatter, splits, kb_per_split));
+    NIB_CUDA(launch_pdl(moe_tc_kernel<TOK, MODE>, dim3((unsigned)(most < sms ? most : sms)), dim3(THREADS), (size_t)C::SMEM, stream, mw, ma, out, ldo,
+                        tiles, n_tiles, max_tiles, src_of, sel_w, top, N, K, w_rows, scatter, splits, kb_per_split, w_out));
     return 0;
 }
 
@@ -431,18 +444,18 @@ NIB_API int nib_moe_gather_rows(const void* src, int lds, void* dst, int ldd, co
     return 0;
 }
 
-// gate_up != 0: A = the rows in the grouped order [a_rows, K], W [experts, 2N, K] (gate rows, then up rows), out bfloat16
-// [a_rows, N]. Else: A [a_rows, K] in the grouped order, W [experts, N, K], out floats: [a_rows, N] in the grouped order, or
+// gate_up 1: A = the rows in the grouped order [a_rows, K], W [experts, 2N, K] (gate rows, then up rows), out bfloat16
+// [a_rows, N]; 2: the same with W [experts, N, K] (no gate) and relu(.)^2. 0: A [a_rows, K] in the grouped order, W [experts, N, K], out floats: [a_rows, N] in the grouped order, or
 // with scatter added into the token's row of [tokens, N] (1: plainly, one choice per token; 2: by reductions in memory).
 // The table must have been made for row tiles of `tile_rows` (32 or 128).
 NIB_API int nib_moe_gemm_tc(int gate_up, const void* A, int lda, int a_rows, const void* W, int experts, void* out, int ldo, const int* tiles,
                             const int* n_tiles, int max_tiles, const int* src_of, const float* sel_w, int top, int N, int K, int scatter,
-                            int tile_rows, cudaStream_t stream) {
+                            int tile_rows, int w_out, cudaStream_t stream) {
     NIB_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && top > 0 && a_rows >= 0 && experts > 0 && max_tiles >= 0 && scatter >= 0 && scatter <= 2
-                && (scatter != 1 || top == 1), "experts (tensor cores): bad sizes");
+                && (scatter != 1 || top == 1) && gate_up >= 0 && gate_up <= 2, "experts (tensor cores): bad sizes");
     NIB_REQUIRE(tile_rows == 32 || tile_rows == 128, "experts (tensor cores): row tiles of 32 or 128, not %d", tile_rows);
     if (max_tiles == 0 || a_rows == 0) return 0;
-    const int w_rows = gate_up ? 2 * N : N;
+    const int w_rows = gate_up == 1 ? 2 * N : N;
     CUtensorMap mw, ma;
     {
         std::lock_guard<std::mutex> lock(g_expert_map_mutex);
@@ -467,10 +480,10 @@ NIB_API int nib_moe_gemm_tc(int gate_up, const void* A, int lda, int a_rows, con
         if (splits > k_blocks / 4) splits = k_blocks / 4;
         if (splits < 1) splits = 1;
     }
-#define NIB_MT(TOK, GU) launch_moe_tc<TOK, GU>(mw, ma, out, ldo, tiles, n_tiles, max_tiles, src_of, sel_w, top, N, K, w_rows, scatter, splits, stream)
+#define NIB_MT(TOK, GU) launch_moe_tc<TOK, GU>(mw, ma, out, ldo, tiles, n_tiles, max_tiles, src_of, sel_w, top, N, K, w_rows, scatter, splits, w_out, stream)
     int rc;
-    if (tile_rows == 32) rc = gate_up ? NIB_MT(32, true) : NIB_MT(32, false);
-    else rc = gate_up ? NIB_MT(128, true) : NIB_MT(128, false);
+    if (tile_rows == 32) rc = gate_up == 1 ? NIB_MT(32, 1) : (gate_up == 2 ? NIB_MT(32, 2) : NIB_MT(32, 0));
+    else rc = gate_up == 1 ? NIB_MT(128, 1) : (gate_up == 2 ? NIB_MT(128, 2) : NIB_MT(128, 0));
 #undef NIB_MT
     if (rc) return rc;
     NIB_LAUNCH_CHECK();

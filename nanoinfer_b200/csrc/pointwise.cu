@@ -521,11 +521,13 @@ NIB_API int nib_gated_norm(const float* o, int ldo, const float* gate, int ldg, 
 // x[t] += mult * y[t] / sqrt(mean(y[t]^2) + eps) * gain: the residual sum of a block whose norm stands on the
 // sublayer's OUTPUT. With `h_out` the new x is also written in the storage type (what the next sublayer reads);
 // with `clear` y is left zeroed, ready for the next sublayer's products to add into. A block per row when rows are
-// few (a decode step), else a warp per row. All arithmetic is 32-bit.
+// few (a decode step), else a warp per row. All arithmetic is 32-bit. With `next_gain` what goes to `h_out` is not the
+// new x but the NEXT sublayer's norm of it, x / sqrt(mean(x^2) + next_eps) * next_gain: a block with a norm before and
+// after each sublayer then makes one pass over the rows per sublayer.
 template <typename T, int THREADS>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_add_kernel(float* __restrict__ y, const float* __restrict__ gain, float* __restrict__ x, T* __restrict__ h_out,
-                   int rows, int width, float eps, float mult, int clear, int vec) {
+                   int rows, int width, float eps, float mult, int clear, int vec, const float* __restrict__ next_gain, float next_eps) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
     __shared__ float part[THREADS / 32];
@@ -553,6 +555,28 @@ rmsnorm_add_kernel(float* __restrict__ y, const float* __restrict__ gain, float*
         for (int w = 0; w < THREADS / 32; ++w) ss += part[w];      // the same order in every thread
     }
     const float scale = mult / sqrtf(ss / (float)width + eps);
+    if (next_gain != nullptr) {
+        // the sum, the sum of squares of the new row, and then the next norm of it
+        float s2 = 0.f;
+        for (int c = first; c < width; c += step) {
+            const float v = xr[c] + yr[c] * scale * gain[c];
+            xr[c] = v;
+            s2 = fmaf(v, v, s2);
+            if (clear) yr[c] = 0.f;
+        }
+        s2 = warp_sum(s2);
+        if (BLOCK_ROW) {
+            __syncthreads();        // every thread has read the first sum's parts
+            if (lane == 0) part[warp] = s2;
+            __syncthreads();
+            s2 = 0.f;
+            for (int w = 0; w < THREADS / 32; ++w) s2 += part[w];
+        }
+        const float scale2 = 1.0f / sqrtf(s2 / (float)width + next_eps);
+        if (h_out != nullptr)
+            for (int c = first; c < width; c += step) Elem<T>::store(h_out + (size_t)row * width + c, xr[c] * scale2 * next_gain[c]);
+        return;
+    }
     if (vec) {
         for (int c = first * 4; c < width; c += step * 4) {
             const float4 yv = *reinterpret_cast<const float4*>(yr + c), g = __ldg(reinterpret_cast<const float4*>(gain + c));
@@ -584,20 +608,69 @@ rmsnorm_add_kernel(float* __restrict__ y, const float* __restrict__ gain, float*
 }
 
 NIB_API int nib_rmsnorm_add(float* y, const float* gain, float* x, void* h_out, int rows, int width, float eps, float mult,
-                            int clear, int dtype, cudaStream_t stream) {
+                            int clear, int dtype, const float* next_gain, float next_eps, cudaStream_t stream) {
     NIB_REQUIRE(rows >= 0 && width > 0, "rmsnorm_add: bad sizes");
     NIB_REQUIRE(dtype == NIB_F32 || dtype == NIB_BF16, "rmsnorm_add: unknown dtype %d", dtype);
     if (rows == 0) return 0;
     const bool block_row = rows <= 64 && width >= 512;
     const int vec = (width % 4 == 0 && (((uintptr_t)y | (uintptr_t)gain | (uintptr_t)x | (uintptr_t)h_out) & 15) == 0) ? 1 : 0;
 #define NIB_RA(T, THREADS, GRID) \
-    NIB_CUDA(launch_pdl(rmsnorm_add_kernel<T, THREADS>, dim3(GRID), dim3(THREADS), (size_t)0, stream, y, gain, x, (T*)h_out, rows, width, eps, mult, clear, vec))
+    NIB_CUDA(launch_pdl(rmsnorm_add_kernel<T, THREADS>, dim3(GRID), dim3(THREADS), (size_t)0, stream, y, gain, x, (T*)h_out, rows, width, eps, mult, clear, vec, next_gain, next_eps))
     if (block_row) {
         if (dtype == NIB_F32) NIB_RA(float, 256, rows); else NIB_RA(__nv_bfloat16, 256, rows);
     } else {
         if (dtype == NIB_F32) NIB_RA(float, 128, ceil_div(rows, 4)); else NIB_RA(__nv_bfloat16, 128, ceil_div(rows, 4));
     }
 #undef NIB_RA
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------- what stands beside routed experts
+// Two per-token steps of a mixture of experts, in one launch of a block per token; either may be absent.
+//  * identity experts: the router outputs from `n_real` on have no weights, their output is the token's input itself, so
+//    out[t] += (sum of the weights of the token's choices e >= n_real) * h[t].
+//  * the activation of an expert that every token uses: act[t, c] = g * relu(u[t, c])^2 (kind 1) or g * u (kind 0), with
+//    g = sigmoid(gate[t * ld_gate]) when a gate logit per token is given, else 1; u is 32-bit, act leaves in T.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_side_kernel(const T* __restrict__ h, int ldh, const int* __restrict__ sel_e, const float* __restrict__ sel_w, int top, int n_real,
+                float* __restrict__ out, int ldo, int hidden, const float* __restrict__ u, int ldu, const float* __restrict__ gate,
+                int ld_gate, T* __restrict__ act, int lda, int ff, int kind) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
+    const int t = blockIdx.x;
+    if (sel_e != nullptr) {
+        float wsum = 0.f;
+        bool any = false;
+        for (int k = 0; k < top; ++k)       // ascending order of choice, the same in every thread
+            if (sel_e[(size_t)t * top + k] >= n_real) { wsum += sel_w[(size_t)t * top + k]; any = true; }
+        if (any)
+            for (int c = threadIdx.x; c < hidden; c += 256) out[(size_t)t * ldo + c] += wsum * Elem<T>::load(h + (size_t)t * ldh + c);
+    }
+    if (act != nullptr) {
+        const float g = gate != nullptr ? 1.0f / (1.0f + expf(-gate[(size_t)t * ld_gate])) : 1.0f;
+        for (int c = threadIdx.x; c < ff; c += 256) {
+            float v = u[(size_t)t * ldu + c];
+            if (kind == 1) { v = fmaxf(v, 0.f); v = v * v; }
+            Elem<T>::store(act + (size_t)t * lda + c, g * v);
+        }
+    }
+}
+
+NIB_API int nib_moe_side(const void* h, int ldh, const int* sel_e, const float* sel_w, int top, int n_real, float* out, int ldo, int hidden,
+                         const float* u, int ldu, const float* gate, int ld_gate, void* act, int lda, int ff, int kind, int tokens, int dtype,
+                         cudaStream_t stream) {
+    NIB_REQUIRE(tokens >= 0 && (sel_e == nullptr || (sel_w != nullptr && out != nullptr && h != nullptr && top > 0 && hidden > 0)) &&
+                (act == nullptr || (u != nullptr && ff > 0 && kind >= 0 && kind <= 1)), "moe_side: bad arguments");
+    NIB_REQUIRE(dtype == NIB_F32 || dtype == NIB_BF16, "moe_side: unknown dtype %d", dtype);
+    if (tokens == 0 || (sel_e == nullptr && act == nullptr)) return 0;
+    if (dtype == NIB_F32)
+        NIB_CUDA(launch_pdl(moe_side_kernel<float>, dim3(tokens), dim3(256), (size_t)0, stream, (const float*)h, ldh, sel_e, sel_w, top, n_real, out, ldo,
+                            hidden, u, ldu, gate, ld_gate, (float*)act, lda, ff, kind));
+    else
+        NIB_CUDA(launch_pdl(moe_side_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), (size_t)0, stream, (const __nv_bfloat16*)h, ldh, sel_e, sel_w, top,
+                            n_real, out, ldo, hidden, u, ldu, gate, ld_gate, (__nv_bfloat16*)act, lda, ff, kind));
     NIB_LAUNCH_CHECK();
     return 0;
 }

@@ -42,6 +42,17 @@ class DecoderModel:
         self.final_norm = _build_part(plan.final_norm, tensors, shared)
         self.head = _build_part(plan.lm_head, tensors, shared)
         self.schedule = list(plan.schedule)
+        # A block that can hand work on to the block after it (``link``) is told which one follows it in the schedule, if
+        # the same one follows wherever the block runs.
+        after: Dict[int, set] = {}
+        for e, nxt in zip(self.schedule, self.schedule[1:] + [None]):
+            after.setdefault(e.layer, set()).add(None if nxt is None else nxt.layer)
+        for idx, layer in enumerate(self.layers):
+            link = getattr(layer, "link", None)
+            if link is not None:
+                followers = after.get(idx, {None})
+                only = next(iter(followers)) if len(followers) == 1 else None
+                link(None if only is None else self.layers[only])
 
     # -- what the cache manager has to provide -------------------------------------------------
     def cache_needs(self) -> List[Tuple[Optional[CacheNeed], Optional[StateNeed], Optional[int]]]:

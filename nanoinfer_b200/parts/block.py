@@ -6,6 +6,9 @@ with the step's earlier streams.
 ``output_norm``: ``x += mult * norm(mixer(x)); x += mult * norm(feed_forward(x))``: the norms stand on the branches'
 outputs, the branches read the stream as it is.
 
+``sandwich_norm``: ``x += norm_b(mixer(norm_a(x))); x += norm_d(feed_forward(norm_c(x)))``: a norm before and after each
+sublayer.
+
 ``pre_norm``: ``x += mixer(norm(x)); x += feed_forward(norm(x))`` with a norm of its own before each
 (cpp/src/model.cpp:364-400, nanoinfer/layers.py:328-339). The residual stream ``x`` is 32-bit and
 both sums are made in 32-bit inside the projections that produce the addends.
@@ -117,6 +120,57 @@ class OutputNormBlock:
             self.ffn_norm.add_normed(y32, x32, self.mult, None if same else h, clear=True)
 
 
+class SandwichNormBlock:
+    """``x <- x + mixer_out_norm(mixer(mixer_norm(x)))``, then ``x <- x + ffn_out_norm(feed_forward(ffn_norm(x)))``: every
+    sublayer reads a norm of the stream and its output is normed again before it is added. parts: ``mixer_norm``,
+    ``mixer``, ``mixer_out_norm`` and optionally ``ffn_norm``, ``ffn``, ``ffn_out_norm`` (all three or none).
+
+    A sublayer adds its result into a zeroed 32-bit buffer as it would into the stream (sums over K splits and over experts
+    included). ONE kernel per sublayer then reads that buffer, norms it, adds it to the 32-bit stream, leaves the buffer
+    zeroed and writes the NEXT sublayer's input norm of the new stream (``add_normed(..., then=)``): the stream is read
+    once per sublayer. Consecutive layers of this arrangement hand the buffer and the next layer's normed input on through
+    the step's scratch, so only the model's first layer runs a norm kernel of its own."""
+
+    part_names = ("mixer_norm", "mixer", "mixer_out_norm", "ffn_norm", "ffn", "ffn_out_norm")
+    _SCRATCH = "sandwich_norm.buffers"
+
+    def __init__(self, parts: Dict[str, object]):
+        self.mixer_norm, self.mixer, self.mixer_out_norm = parts["mixer_norm"], parts["mixer"], parts["mixer_out_norm"]
+        self.ffn_norm, self.ffn, self.ffn_out_norm = parts.get("ffn_norm"), parts.get("ffn"), parts.get("ffn_out_norm")
+        if len({self.ffn_norm is None, self.ffn is None, self.ffn_out_norm is None}) != 1:
+            raise ValueError("a feed-forward comes with the norm before it and the norm on its output")
+        self.part_names = tuple(n for n in SandwichNormBlock.part_names if parts.get(n) is not None)
+        self.next_block = None      # the block that runs next in the schedule, when it is of this kind (set by link())
+
+    def link(self, following) -> None:
+        """Told once after construction which block follows in the schedule (None at the end): when it is of this kind, the
+        last norm kernel of this block also writes that block's first input."""
+        self.next_block = following if isinstance(following, SandwichNormBlock) else None
+
+    def forward(self, x32: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
+        rt = self.mixer.rt
+        held = ctx.scratch.pop(self._SCRATCH, None)
+        if held is not None and held[0] is x32 and held[3] is self:
+            _, y32, h = held[:3]
+        else:
+            y32 = torch.zeros_like(x32)
+            h = self.mixer_norm.forward(x32)
+        self.mixer.forward(h, y32, ctx, cache)
+        nxt = self.next_block
+        if self.ffn is not None:
+            self.mixer_out_norm.add_normed(y32, x32, 1.0, h, clear=True, then=self.ffn_norm)
+            self.ffn.forward(h, y32, ctx)
+            last = self.ffn_out_norm
+        else:
+            last = self.mixer_out_norm
+        if nxt is not None:
+            last.add_normed(y32, x32, 1.0, h, clear=True, then=nxt.mixer_norm)
+            ctx.scratch[self._SCRATCH] = (x32, y32, h, nxt)
+        else:
+            last.add_normed(y32, x32, 1.0, None, clear=False)
+
+
 register_arrangement("pre_norm", PreNormBlock)
+register_arrangement("sandwich_norm", SandwichNormBlock)
 register_arrangement("output_norm", OutputNormBlock)
 register_arrangement("parallel", ParallelBlock)

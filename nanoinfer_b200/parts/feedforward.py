@@ -80,54 +80,128 @@ class PolyNormFeedForward(FeedForward):
 
 
 class RoutedExperts(FeedForward):
-    """A mixture of experts: ``experts`` gated feed-forwards ``W_down (silu(W_gate x) * (W_up x))`` without biases, of
-    which every token uses ``top``. Router: logits ``z = W_router h`` in 32-bit, scores ``sigmoid(z)``; the ``top`` largest
-    are chosen (the first of equal ones); a chosen expert's score is its weight, as it is (``renormalize`` is not among
-    the options), and it multiplies the expert's INPUT: the output is ``sum_e expert_e(score_e * h)``, added to the
-    residual stream.
+    """A mixture of experts: ``experts`` small feed-forwards without biases, of which every token uses ``top``. Router: logits
+    ``z = W_router h`` in 32-bit; the ``top`` outputs with the largest scores are chosen (the first of equal ones); the
+    result, the weighted sum of the chosen experts, is added to the residual stream.
 
-    params: ``hidden``, ``ff`` (an expert's inner width), ``experts``, ``top``. tensors: ``router [experts, hidden]`` and per
-    expert i ``e<i>_gate, e<i>_up [ff, hidden]``, ``e<i>_down [hidden, ff]``; they are stacked once at load into
-    ``[experts, 2 ff, hidden]`` (gate rows, then up rows) and ``[experts, hidden, ff]``."""
+    The form without options: experts ``W_down (silu(W_gate x) * (W_up x))``, scores ``sigmoid(z)``, a chosen expert's score is
+    its weight as it is, and it multiplies the expert's INPUT: ``sum_e expert_e(score_e * h)``.
+
+    Options (params):
+
+    * ``score`` "softmax": the scores are the softmax of a token's logits over ALL router outputs;
+    * ``correction``: a stored number per router output is added to the scores for the CHOICE only; the weights are the
+      scores without it;
+    * ``renormalize``: the chosen scores are divided by their sum (+ 1e-20);
+    * ``weight_on`` "output": the weight multiplies the expert's result, ``sum_e score_e * expert_e(h)``;
+    * ``gated`` False: an expert is ``W_down relu(W_up x)^2`` (tensors ``e<i>_up``, ``e<i>_down``);
+    * ``identity`` n: the router has n more outputs behind the experts' that stand for no weights: such a choice adds
+      ``weight * h``;
+    * ``shared`` ff: one more expert of the experts' form, ``ff`` wide, that every token uses; its result is multiplied by
+      ``sigmoid(W_sg h)``, one number per token (tensors ``shared_up``, ``shared_down``, ``shared_sg [1, hidden]``; for
+      experts without a gate). Its gate logit is one more row of the router's product.
+
+    params: ``hidden``, ``ff`` (an expert's inner width), ``experts``, ``top`` and the options. tensors: ``router [experts +
+    identity, hidden]`` and per expert i ``e<i>_gate, e<i>_up [ff, hidden]``, ``e<i>_down [hidden, ff]``; they are stacked once at
+    load into ``[experts, 2 ff, hidden]`` (gate rows, then up rows; ``[experts, ff, hidden]`` without gates) and
+    ``[experts, hidden, ff]``."""
 
     graph_safe = True   # the launches depend on the token count alone: the tile table of the routing lives on the device
 
     @staticmethod
-    def spec(prefix: str, hidden: int, ff: int, experts: int, top: int) -> PartSpec:
-        t = {"router": TensorSpec(f"{prefix}.router", (experts, hidden))}
+    def spec(prefix: str, hidden: int, ff: int, experts: int, top: int, *, score: str = "sigmoid", correction: bool = False,
+             renormalize: bool = False, weight_on: str = "input", gated: bool = True, identity: int = 0, shared: int = 0) -> PartSpec:
+        t = {"router": TensorSpec(f"{prefix}.router", (experts + identity, hidden))}
+        if correction:
+            t["correction"] = TensorSpec(f"{prefix}.correction", (experts + identity,), "bias")
         for i in range(experts):
-            t[f"e{i}_gate"] = TensorSpec(f"{prefix}.e{i}.gate", (ff, hidden))
+            if gated:
+                t[f"e{i}_gate"] = TensorSpec(f"{prefix}.e{i}.gate", (ff, hidden))
             t[f"e{i}_up"] = TensorSpec(f"{prefix}.e{i}.up", (ff, hidden))
             t[f"e{i}_down"] = TensorSpec(f"{prefix}.e{i}.down", (hidden, ff))
-        return PartSpec("routed_experts", {"hidden": hidden, "ff": ff, "experts": experts, "top": top}, t)
+        if shared:
+            t["shared_up"] = TensorSpec(f"{prefix}.shared.up", (shared, hidden))
+            t["shared_down"] = TensorSpec(f"{prefix}.shared.down", (hidden, shared))
+            t["shared_sg"] = TensorSpec(f"{prefix}.shared.sg", (1, hidden))
+        params = {"hidden": hidden, "ff": ff, "experts": experts, "top": top}
+        options = {"score": score, "correction": bool(correction), "renormalize": bool(renormalize), "weight_on": weight_on,
+                   "gated": bool(gated), "identity": int(identity), "shared": int(shared)}
+        defaults = {"score": "sigmoid", "correction": False, "renormalize": False, "weight_on": "input", "gated": True, "identity": 0, "shared": 0}
+        params.update({k: v for k, v in options.items() if v != defaults[k]})
+        return PartSpec("routed_experts", params, t)
 
     def __init__(self, spec: PartSpec, tensors: Dict[str, torch.Tensor], rt: Runtime):
         super().__init__(spec, tensors, rt)
         p = spec.params
         self.hidden, self.ff = int(p["hidden"]), int(p["ff"])
         self.experts, self.top = int(p["experts"]), int(p["top"])
-        if not (1 <= self.top <= self.experts):
-            raise ValueError(f"a token uses {self.top} of {self.experts} experts")
-        self.w_router = rt.matrix(tensors["router"])
-        self.w_gate_up = rt.matrix(torch.stack([torch.cat([tensors[f"e{i}_gate"], tensors[f"e{i}_up"]], dim=0)
-                                                for i in range(self.experts)]))
+        self.score, self.renormalize = str(p.get("score", "sigmoid")), bool(p.get("renormalize", False))
+        self.weight_on, self.gated = str(p.get("weight_on", "input")), bool(p.get("gated", True))
+        self.identity, self.shared = int(p.get("identity", 0)), int(p.get("shared", 0))
+        self.outputs = self.experts + self.identity         # what the router chooses among
+        if not (1 <= self.top <= self.outputs):
+            raise ValueError(f"a token uses {self.top} of {self.outputs} router outputs")
+        if self.score not in ("sigmoid", "softmax") or self.weight_on not in ("input", "output"):
+            raise ValueError(f"unknown router score '{self.score}' or place of the weight '{self.weight_on}'")
+        if self.shared and self.gated:
+            raise ValueError("an expert that every token uses is built for experts without a gate")
+        # the shared expert's gate logit is one more row of the router's product
+        rows = [tensors["router"]] + ([tensors["shared_sg"]] if self.shared else [])
+        self.w_router = rt.matrix(torch.cat(rows, dim=0))
+        self.correction = rt.vector32(tensors["correction"]) if p.get("correction") else None
+        first = (lambda i: torch.cat([tensors[f"e{i}_gate"], tensors[f"e{i}_up"]], dim=0)) if self.gated else (lambda i: tensors[f"e{i}_up"])
+        self.w_gate_up = rt.matrix(torch.stack([first(i) for i in range(self.experts)]))
         self.w_down = rt.matrix(torch.stack([tensors[f"e{i}_down"] for i in range(self.experts)]))
+        if self.shared:
+            self.w_shared_up = rt.matrix(tensors["shared_up"])
+            self.w_shared_down = rt.matrix(tensors["shared_down"])
+        self.plain = self.score == "sigmoid" and not self.renormalize and self.correction is None and self.weight_on == "input" \
+            and self.gated and not self.identity and not self.shared
 
     def forward(self, h, residual32: torch.Tensor, ctx: StepContext) -> None:
         h = as_tensor(h)
         m, dev = h.shape[0], h.device
         chosen = torch.empty((m, self.top), dtype=torch.int32, device=dev)
         weight = torch.empty((m, self.top), dtype=torch.float32, device=dev)
-        # a short step (decoding): router, choice and grouping are one launch where the backend has one
-        step = getattr(self.ops, "moe_step", None)
-        plan = step(h, self.w_router, self.top, self.w_gate_up, self.w_down, chosen, weight) if step is not None else None
-        if plan is not None:
-            self.ops.moe_experts(h, chosen, weight, self.w_gate_up, self.w_down, residual32, plan=plan)
+        if self.plain:
+            # a short step (decoding): router, choice and grouping are one launch where the backend has one
+            step = getattr(self.ops, "moe_step", None)
+            plan = step(h, self.w_router, self.top, self.w_gate_up, self.w_down, chosen, weight) if step is not None else None
+            if plan is not None:
+                self.ops.moe_experts(h, chosen, weight, self.w_gate_up, self.w_down, residual32, plan=plan)
+                return
+            z32 = torch.empty((m, self.experts), dtype=torch.float32, device=dev)
+            self.ops.linear(h, self.w_router, None, z32, "f32")
+            self.ops.moe_route(z32, self.top, chosen, weight)
+            self.ops.moe_experts(h, chosen, weight, self.w_gate_up, self.w_down, residual32)
             return
-        z32 = torch.empty((m, self.experts), dtype=torch.float32, device=dev)
-        self.ops.linear(h, self.w_router, None, z32, "f32")
-        self.ops.moe_route(z32, self.top, chosen, weight)
-        self.ops.moe_experts(h, chosen, weight, self.w_gate_up, self.w_down, residual32)
+        extra = 1 if self.shared else 0
+        options = dict(score=self.score, renormalize=self.renormalize, correction32=self.correction)
+        step = getattr(self.ops, "moe_step", None)
+        gate32 = torch.empty((m, extra), dtype=torch.float32, device=dev) if extra else None
+        plan = step(h, self.w_router, self.top, self.w_gate_up, self.w_down, chosen, weight, n_real=self.experts, extra=extra,
+                    z_extra=gate32, **options) if step is not None else None
+        if plan is None:
+            z32 = torch.empty((m, self.outputs + extra), dtype=torch.float32, device=dev)
+            self.ops.linear(h, self.w_router, None, z32, "f32")
+            self.ops.moe_route(z32[:, :self.outputs], self.top, chosen, weight, **options)
+            gate32 = z32[:, self.outputs:] if extra else None
+        self.ops.moe_experts(h, chosen, weight, self.w_gate_up, self.w_down, residual32, plan=plan, gated=self.gated,
+                             weight_on=self.weight_on, outputs=self.outputs)
+        if not self.shared:
+            if self.identity:
+                self.ops.moe_side(h, residual32, chosen, weight, self.experts)
+            return
+        # the expert that every token uses: its first product, then (one launch) its activation times the token's gate and the
+        # identity choices' share, then its down product into the stream
+        act = torch.empty((m, self.shared), dtype=self.rt.dtype, device=dev)
+        u32 = torch.empty((m, self.shared), dtype=torch.float32, device=dev)
+        self.ops.linear(h, self.w_shared_up, None, u32, "f32")
+        if self.identity:
+            self.ops.moe_side(h, residual32, chosen, weight, self.experts, u32=u32, act=act, gate32=gate32, kind="relu2")
+        else:
+            self.ops.moe_side(h, u32=u32, act=act, gate32=gate32, kind="relu2")
+        self.ops.linear(act, self.w_shared_down, None, residual32, "add")
 
 
 register_part("routed_experts", RoutedExperts)

@@ -7,7 +7,11 @@ With ``q = W_q h + b_q`` (likewise k, v), in this order:
 * convolution (``conv`` taps > 0): ``y_t = sum_j w[:, j] u_(t - taps + 1 + j)`` per channel, zeros before the request's
   start; the request's last ``taps - 1`` projected rows are kept in its state;
 * ``qk_norm``: every head of q and k is divided by its root mean square (``eps`` inside the root) and multiplied by a
-  gain of the head's size that all heads share;
+  gain of the head's size that all heads share; with ``qk_norm`` = "whole" the root mean square is taken over ALL heads
+  of a token's q (and of its k) at once, before they are split into heads, and the gains have the projections' sizes;
+* ``v_mix``: the layers of a model that set it share the values of the first of them: that one ("first") leaves its
+  projected values of the step's tokens for the later ones ("blend"), whose values become
+  ``(1 - lambda) v + lambda v_first`` with a learned number ``lambda`` each; the blend is what is cached;
 * ``rot`` = (dims, base): the first ``dims`` elements of every q and k head are turned by ``position * base^(-2i/dims)``,
   element i paired with i + dims/2 (``rot_layout`` "half") or 2i with 2i + 1 ("interleaved"); with ``rot_factor`` f
   every frequency is divided by f (linear position scaling); the angle is formed in 32-bit;
@@ -18,7 +22,8 @@ With ``q = W_q h + b_q`` (likewise k, v), in this order:
   ``2^(-s (h + 1) / H) * (i - j)`` at distance i - j;
 * position i sees j <= i; with ``window`` w only j > i - w; with ``chunk`` c only ``floor(j / c) == floor(i / c)``,
   counted from the request's position 0;
-* softmax in 32-bit, weighted sum of v (``vdim`` wide), times ``sigmoid(W_g h)`` with ``out_gate``, then
+* softmax in 32-bit; with ``sink`` the denominator holds ``exp(sink_h)`` once more, a learned number per head without
+  key or value, neither scaled nor capped; weighted sum of v (``vdim`` wide), times ``sigmoid(W_g h)`` with ``out_gate``, then
   ``out_scale * (W_o . + b_o)`` is added to the residual stream.
 
 What is cached per position is the key after convolution, norm and rotation, and the value after convolution.
@@ -43,17 +48,20 @@ def rotary_frequencies(dims: int, base: float, factor: float = 1.0) -> torch.Ten
 class FlexAttention(Mixer):
     """params: ``hidden heads kv_heads dim vdim scale eps`` and the options ``bias`` (q, k, v), ``out_bias``, ``conv``
     (taps), ``qk_norm``, ``rot`` ((dims, base) or None), ``softcap``, ``slope_span``, ``window``, ``chunk``,
-    ``out_gate``, ``out_scale``, ``rot_layout``, ``rot_factor``, ``unit_norm_after_rot``, ``values_from_keys``. tensors:
-    ``q k o``, ``v`` unless the values are the keys, and, by option, ``q_b k_b v_b o_b q_conv k_conv v_conv q_norm k_norm g``."""
+    ``out_gate``, ``out_scale``, ``rot_layout``, ``rot_factor``, ``unit_norm_after_rot``, ``values_from_keys``, ``sink``,
+    ``v_mix`` (None, "first" or "blend"). tensors: ``q k o``, ``v`` unless the values are the keys, and, by option,
+    ``q_b k_b v_b o_b q_conv k_conv v_conv q_norm k_norm g sink vmix``."""
 
     graph_safe = True   # launches do not depend on which requests are in the batch
+    V_FIRST = "flex_attention.v_first"      # key of the step's scratch under which the first v_mix layer leaves its values
 
     @staticmethod
     def spec(prefix: str, hidden: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, eps: float, *,
              bias: bool = False, out_bias: bool = False, conv: int = 0, qk_norm: bool = False, rot=None,
              softcap: float = 0.0, slope_span: float = 0.0, window: int = 0, chunk: int = 0, out_gate: bool = False,
              out_scale: float = 1.0, rot_layout: str = "half", rot_factor: float = 1.0, unit_norm_after_rot: bool = False,
-             values_from_keys: bool = False) -> PartSpec:
+             values_from_keys: bool = False, sink: bool = False, v_mix=None) -> PartSpec:
+        """``qk_norm``: False, True (per head, a gain of the head's size) or "whole"."""
         nq, nk, nv = heads * dim, kv_heads * dim, kv_heads * vdim
         t = {"q": TensorSpec(f"{prefix}.q", (nq, hidden)), "k": TensorSpec(f"{prefix}.k", (nk, hidden)),
              "v": TensorSpec(f"{prefix}.v", (nv, hidden)), "o": TensorSpec(f"{prefix}.o", (hidden, heads * vdim))}
@@ -70,8 +78,12 @@ class FlexAttention(Mixer):
             for name, n in projected:
                 t[name + "_conv"] = TensorSpec(f"{prefix}.{name}.conv", (n, conv), "unit")
         if qk_norm:
-            t["q_norm"] = TensorSpec(f"{prefix}.q.norm", (dim,), "gain")
-            t["k_norm"] = TensorSpec(f"{prefix}.k.norm", (dim,), "gain")
+            t["q_norm"] = TensorSpec(f"{prefix}.q.norm", (nq if qk_norm == "whole" else dim,), "gain")
+            t["k_norm"] = TensorSpec(f"{prefix}.k.norm", (nk if qk_norm == "whole" else dim,), "gain")
+        if sink:
+            t["sink"] = TensorSpec(f"{prefix}.sink", (heads,), "unit")
+        if v_mix == "blend":
+            t["vmix"] = TensorSpec(f"{prefix}.vmix", (), "mix01")
         if out_gate:
             t["g"] = TensorSpec(f"{prefix}.g", (heads * vdim, hidden))
         params = {"hidden": hidden, "heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": float(scale),
@@ -79,7 +91,8 @@ class FlexAttention(Mixer):
                   "rot": None if rot is None else (int(rot[0]), float(rot[1])), "softcap": float(softcap),
                   "slope_span": float(slope_span), "window": int(window), "chunk": int(chunk), "out_gate": out_gate,
                   "out_scale": float(out_scale), "rot_layout": str(rot_layout), "rot_factor": float(rot_factor),
-                  "unit_norm_after_rot": bool(unit_norm_after_rot), "values_from_keys": bool(values_from_keys)}
+                  "unit_norm_after_rot": bool(unit_norm_after_rot), "values_from_keys": bool(values_from_keys),
+                  "sink": bool(sink), "v_mix": v_mix}
         return PartSpec("flex_attention", params, t)
 
     def __init__(self, spec: PartSpec, tensors: Dict[str, torch.Tensor], rt: Runtime):
@@ -117,6 +130,12 @@ class FlexAttention(Mixer):
         self.conv_w = rt.vector32(torch.cat([tensors[n + "_conv"] for n in named], dim=0)) if self.taps else None
         self.q_gain = rt.vector32(tensors["q_norm"]) if p.get("qk_norm") else None
         self.k_gain = rt.vector32(tensors["k_norm"]) if p.get("qk_norm") else None
+        self.norm_whole = p.get("qk_norm") == "whole"
+        self.sinks = rt.vector32(tensors["sink"]) if p.get("sink") else None
+        self.v_mix = p.get("v_mix")
+        if self.v_mix not in (None, "first", "blend") or (self.v_mix and self.values_from_keys):
+            raise ValueError(f"v_mix is None, 'first' or 'blend' (and needs values of its own), not {self.v_mix!r}")
+        self.vmix = rt.vector32(tensors["vmix"].reshape(1)) if self.v_mix == "blend" else None
         rot = p.get("rot")
         self.rot_dims = 0 if rot is None else int(rot[0])
         if self.rot_dims % 2 or self.rot_dims > self.dim:
@@ -151,16 +170,23 @@ class FlexAttention(Mixer):
             ops.conv_step(qkv32, self.conv_w, None, "none", cache.state, 0, ctx, conv32, self.taps)
             qkv32 = conv32
         q = torch.empty((m, self.nq), dtype=self.rt.dtype, device=dev)
+        v_first = None
+        if self.v_mix == "first":       # kept alive by the step's scratch until the last layer that blends has read it
+            ctx.scratch[self.V_FIRST] = qkv32[:, self.nq + self.nk:]
+        elif self.v_mix == "blend":
+            v_first = ctx.scratch.get(self.V_FIRST)
+            if v_first is None or tuple(v_first.shape) != (m, self.nv):
+                raise ValueError("a layer that blends its values found no values of the same shape left by an earlier layer of this step")
         # norm, rotation, queries in the storage type, keys and values into their pages
         ops.attention_prepare(qkv32, q, self.heads, self.kv_heads, self.dim, self.vdim, self.q_gain, self.k_gain, self.eps,
                               self.freq, self.rot_dims, ctx, cache.block_table, cache.page_size, cache.pages["k"], cache.pages["v"],
                               cache.writes, layout=self.rot_layout, unit_norm_after=self.unit_norm_after,
-                              values_are_keys=self.values_from_keys)
+                              values_are_keys=self.values_from_keys, norm_whole=self.norm_whole, v_first32=v_first, vmix32=self.vmix)
         gated = self.out_gate
         attn = torch.empty((m, self.heads * self.vdim), dtype=torch.float32 if gated else self.rt.dtype, device=dev)
         ops.attention_flex(q, attn, self.heads, self.kv_heads, self.dim, self.vdim, self.scale, self.softcap, self.slopes,
                            self.window, self.chunk, 1.0 if gated else self.out_scale, ctx, cache.block_table, cache.page_size,
-                           cache.pages["k"], cache.pages["v"])
+                           cache.pages["k"], cache.pages["v"], sinks32=self.sinks)
         if gated:
             a = torch.empty((m, self.heads * self.vdim), dtype=self.rt.dtype, device=dev)
             ops.gated_norm(attn, a, gate32=p32[:, self.n_qkv:], gate_kind="sigmoid", out_scale=self.out_scale)

@@ -101,3 +101,4 @@ def _ensure_builtin() -> None:
     from .models import nezalorn as _nezalorn  # noqa: F401  registers Nezalorn
     from .models import vafozen as _vafozen  # noqa: F401  registers Vafozen
     from .models import darotar as _darotar  # noqa: F401  registers Darotar
+    from .models import dusilorn as _dusilorn  # noqa: F401  registers Dusilorn

@@ -135,13 +135,20 @@ class TorchOps:
     # ---- attention with options (attention_flex.cu) --------------------------------------------------
     def attention_prepare(self, qkv32, q_out, heads, kv_heads, dim, vdim, q_gain32, k_gain32, eps, freq32, rot_dims, ctx,
                           block_table, page_size, k_pages, v_pages, writes, layout="half", unit_norm_after=False,
-                          values_are_keys=False):
+                          values_are_keys=False, norm_whole=False, v_first32=None, vmix32=None):
         m = qkv32.shape[0]
         nq, nk = heads * dim, kv_heads * dim
         q = qkv32[:, :nq].double().reshape(m, heads, dim)
         k = qkv32[:, nq:nq + nk].double().reshape(m, kv_heads, dim)
         v = k.clone() if values_are_keys else qkv32[:, nq + nk:].double().reshape(m, kv_heads, vdim)
-        if q_gain32 is not None:
+        if v_first32 is not None:
+            lam = vmix32.double().reshape(())
+            v = (1.0 - lam) * v + lam * v_first32.double().reshape(m, kv_heads, vdim)
+        if q_gain32 is not None and norm_whole:
+            qf, kf = q.reshape(m, nq), k.reshape(m, nk)
+            q = (qf / torch.sqrt(qf.pow(2).mean(-1, keepdim=True) + eps) * q_gain32.double()).reshape(m, heads, dim)
+            k = (kf / torch.sqrt(kf.pow(2).mean(-1, keepdim=True) + eps) * k_gain32.double()).reshape(m, kv_heads, dim)
+        elif q_gain32 is not None:
             q = q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_gain32.double()
             k = k / torch.sqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_gain32.double()
         if rot_dims:
@@ -172,7 +179,7 @@ class TorchOps:
         v_pages[page[ok], :, (pos % page_size)[ok], :] = v[ok].to(v_pages.dtype)
 
     def attention_flex(self, q, out, heads, kv_heads, dim, vdim, scale, softcap, slopes32, window, chunk, out_scale, ctx,
-                       block_table, page_size, k_pages, v_pages):
+                       block_table, page_size, k_pages, v_pages, sinks32=None):
         m = q.shape[0]
         qh = q.double().view(m, heads, dim)
         rep = heads // kv_heads
@@ -194,7 +201,11 @@ class TorchOps:
                     s = softcap * torch.tanh(s / softcap)
                 if slopes32 is not None:
                     s = s - slopes32[h].double() * (pos - js).double()
-                res[t, h] = torch.softmax(s, 0) @ v[:, h // rep]
+                if sinks32 is not None:     # one more term of the denominator, with no value
+                    w = torch.softmax(torch.cat([s, sinks32[h].double().reshape(1)]), 0)[:-1]
+                else:
+                    w = torch.softmax(s, 0)
+                res[t, h] = w @ v[:, h // rep]
         out.copy_((res.view(m, heads * vdim) * out_scale).to(out.dtype))
 
     # ---- gate, norm in groups, skip (pointwise.cu) ---------------------------------------------------
@@ -419,31 +430,62 @@ class TorchOps:
         out.copy_(v.to(out.dtype))
 
     # ---- the norm on a branch's output, and routed experts (pointwise.cu, moe.cu) -----------------------------
-    def rmsnorm_add(self, y32, gain32, eps, mult, x32, h_out=None, clear=False):
+    def rmsnorm_add(self, y32, gain32, eps, mult, x32, h_out=None, clear=False, next_gain32=None, next_eps=0.0):
         y = y32.double()
         x = x32.double() + mult * y / torch.sqrt(y.pow(2).mean(-1, keepdim=True) + eps) * gain32.double()
         x32.copy_(x.to(torch.float32))
-        if h_out is not None:
+        if h_out is not None and next_gain32 is not None:
+            xn = x32.double()
+            h_out.copy_((xn / torch.sqrt(xn.pow(2).mean(-1, keepdim=True) + next_eps) * next_gain32.double()).to(h_out.dtype))
+        elif h_out is not None:
             h_out.copy_(x32.to(h_out.dtype))
         if clear:
             y32.zero_()
 
-    def moe_route(self, z32, top, sel_e, sel_w):
-        order = torch.sort(z32.double(), dim=-1, descending=True, stable=True).indices[:, :top]
+    def moe_route(self, z32, top, sel_e, sel_w, score="sigmoid", renormalize=False, correction32=None):
+        z = z32.double()
+        if score == "sigmoid" and not renormalize and correction32 is None:
+            order = torch.sort(z, dim=-1, descending=True, stable=True).indices[:, :top]
+            sel_e.copy_(order.to(torch.int32))
+            sel_w.copy_(torch.sigmoid(torch.gather(z, 1, order)).to(torch.float32))
+            return
+        sc = torch.softmax(z, -1) if score == "softmax" else torch.sigmoid(z)
+        choice = sc if correction32 is None else sc + correction32.double()
+        order = torch.sort(choice, dim=-1, descending=True, stable=True).indices[:, :top]
+        w = torch.gather(sc, 1, order)
+        if renormalize:
+            w = w / (w.sum(-1, keepdim=True) + 1e-20)
         sel_e.copy_(order.to(torch.int32))
-        sel_w.copy_(torch.sigmoid(torch.gather(z32.double(), 1, order)).to(torch.float32))
+        sel_w.copy_(w.to(torch.float32))
 
-    def moe_experts(self, h, sel_e, sel_w, w_gate_up, w_down, out32):
-        ff = w_gate_up.shape[1] // 2
+    def moe_experts(self, h, sel_e, sel_w, w_gate_up, w_down, out32, plan=None, gated=True, weight_on="input", outputs=None):
+        ff = w_down.shape[2]
         acc = out32.double()
         for t in range(h.shape[0]):
             for c in range(sel_e.shape[1]):
                 e, w = int(sel_e[t, c]), sel_w[t, c].double()
-                g = (w_gate_up[e, :ff].double() @ h[t].double()) * w
-                u = (w_gate_up[e, ff:].double() @ h[t].double()) * w
-                act = (g / (1.0 + torch.exp(-g)) * u).to(h.dtype).double()
-                acc[t] += w_down[e].double() @ act
+                if e >= w_down.shape[0]:
+                    continue        # a router output that is no expert
+                w_in, w_res = (w, 1.0) if weight_on == "input" else (1.0, w)
+                if gated:
+                    g = (w_gate_up[e, :ff].double() @ h[t].double()) * w_in
+                    u = (w_gate_up[e, ff:].double() @ h[t].double()) * w_in
+                    act = (g / (1.0 + torch.exp(-g)) * u).to(h.dtype).double()
+                else:
+                    act = (torch.relu((w_gate_up[e].double() @ h[t].double()) * w_in) ** 2).to(h.dtype).double()
+                acc[t] += w_res * (w_down[e].double() @ act)
         out32.copy_(acc.to(torch.float32))
+
+    def moe_side(self, h, out32=None, sel_e=None, sel_w=None, n_real=0, u32=None, act=None, gate32=None, kind="relu2"):
+        if sel_e is not None:
+            w = (sel_w.double() * (sel_e >= n_real)).sum(-1, keepdim=True)
+            out32.copy_((out32.double() + w * h.double()).to(torch.float32))
+        if act is not None:
+            u = u32.double()
+            f = torch.relu(u) ** 2 if kind == "relu2" else u
+            if gate32 is not None:
+                f = f * torch.sigmoid(gate32.double().reshape(-1, 1))
+            act.copy_(f.to(act.dtype))
 
     def argmax(self, logits, out):
         out.copy_(torch.argmax(logits, dim=-1).to(out.dtype))
