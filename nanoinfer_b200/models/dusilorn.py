@@ -94,8 +94,8 @@ class DusilornConfig(ModelConfig):
                 raise ConfigError(f"config.json: {where}.heads must be a multiple of kv_heads")
             vdim = _int(m, "vdim", where) if "vdim" in m else dim
             _num(m, "scale", where)
-            if m.get("softcap") is not None:
-                _num(m, "softcap", where)
+            if m.get("softcap") is not None and _num(m, "softcap", where, positive=False) < 0:      # 0: the scores are not capped
+                raise ConfigError(f"config.json: {where}.softcap must not be negative")
             _mask(m, where)
             if layer["type"] == "attention_2":
                 rot = _obj(m, "rot", where)
