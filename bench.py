@@ -558,8 +558,40 @@ def darotar_configs(size: dict):
     return dar, design_configs(dict(DESIGN_SIZES["1k"], **{k: size[k] for k in ("width", "heads", "head_dim", "ff_swiglu", "vocab", "layers")}))[1]
 
 
+# A Dusilorn stack at the same widths: rotated attention behind a sliding window and chunked attention with a sink and a
+# norm of q and k over the whole projection, by turns, all with the Qwen2 decoder's head counts and head size and with
+# blended values; the first feed-forward dense, the others mixtures of 8 experts without a gate (relu squared, two
+# matrices each) and one identity output, of which a token uses 2, beside a shared expert: the chosen experts and the
+# shared one are half as wide as the Qwen2 decoder's feed-forward each, so a token passes through as many feed-forward
+# parameters in both models (2 x 2 + 2 halves against 3 matrices).
+DUSILORN_SIZES = {
+    "1k": {"width": 1024, "heads": 16, "head_dim": 64, "ff_swiglu": 2816, "rot": 32, "experts": 8, "identity": 1, "top": 2,
+           "window": 1024, "vocab": 32000, "layers": 8},
+    "2k": {"width": 2048, "heads": 16, "head_dim": 128, "ff_swiglu": 5632, "rot": 64, "experts": 8, "identity": 1, "top": 2,
+           "window": 1024, "vocab": 32000, "layers": 8},
+}
+
+
+def dusilorn_configs(size: dict):
+    w, h, d = size["width"], size["heads"], size["head_dim"]
+    half = size["ff_swiglu"] // 2
+    ff = {"kind": "moe", "expert": {"ff": half}, "router": {"experts": size["experts"], "identity": size["identity"], "top": size["top"]},
+          "shared": {"ff": half}}
+    common = {"heads": h, "kv_heads": 2, "dim": d, "vdim": d, "scale": d ** -0.5, "softcap": 30.0, "v_mix": True, "mask": {"size": size["window"]}}
+    layers = []
+    for i in range(size["layers"]):
+        mlp = {"kind": "dense", "ff": size["ff_swiglu"]} if i == 0 else ff
+        if i % 2:
+            layers.append({"type": "attention", "mixer": dict(common), "mlp": mlp})
+        else:
+            layers.append({"type": "attention_2", "mixer": dict(common, rot={"dims": size["rot"], "base": 1000000.0}), "mlp": mlp})
+    dus = {"architecture": "Dusilorn", "vocab": size["vocab"], "width": w, "norm": {"eps": 1e-5}, "embedding": {"scale": 8.0},
+           "logit_scale": 0.5, "layers": layers}
+    return dus, design_configs(dict(DESIGN_SIZES["1k"], **{k: size[k] for k in ("width", "heads", "head_dim", "ff_swiglu", "vocab", "layers")}))[1]
+
+
 def run_design(args) -> dict:
-    """Prefill and decode throughput of a design (Nezalorn, Vafozen, Darotar) beside the Qwen2 decoder at equal size (random
+    """Prefill and decode throughput of a design (Nezalorn, Vafozen, Darotar, Dusilorn) beside the Qwen2 decoder at equal size (random
     weights, bfloat16, device-timed with CUDA events), and where one eager step's time goes, launch kind by launch kind."""
     import numpy as np
     import torch
@@ -572,7 +604,7 @@ def run_design(args) -> dict:
     steps, warmup = min(args.steps, 64), max(3, args.warmup)
     design = args.design
     sizes, configs = {"nezalorn": (DESIGN_SIZES, design_configs), "vafozen": (VAFOZEN_SIZES, vafozen_configs),
-                      "darotar": (DAROTAR_SIZES, darotar_configs)}[design]
+                      "darotar": (DAROTAR_SIZES, darotar_configs), "dusilorn": (DUSILORN_SIZES, dusilorn_configs)}[design]
     out = {"impl": "ours", "design": design, "dtype": "bf16", "data": "synthetic: seeded random weights and random token ids",
            "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk["source"]},
            "config": {"prefill_tokens": t_pre, "decode_batch": batch, "decode_context": ctx, "page_size": 16}, "sizes": {}}
@@ -804,7 +836,7 @@ def main() -> int:
                     help="add a 'kernels' block: where the time of a decode step and of a prompt portion goes, kernel kind by "
                          "kind, with bytes or FLOPs and the fraction of the measured peak")
     ap.add_argument("--shape", default="0.5b", choices=sorted(SHAPES), help="layer sizes: the family's 0.5B (default), 1.5B or 7B")
-    ap.add_argument("--design", default=None, choices=["nezalorn", "vafozen", "darotar"],
+    ap.add_argument("--design", default=None, choices=["nezalorn", "vafozen", "darotar", "dusilorn"],
                     help="instead of the headline workload: prefill and decode throughput of this design beside the Qwen2 "
                          "decoder at equal size (--design-sizes, --prefill-tokens, --batch, --context up to 2048, --breakdown)")
     ap.add_argument("--design-sizes", default="", help="comma-separated names of DESIGN_SIZES (default: all)")

@@ -26,22 +26,16 @@ constexpr int FX_WARPS = 4;
 // flags of attention_prepare
 enum { FXP_INTERLEAVED = 1, FXP_UNIT_NORM_AFTER = 2, FXP_VALUES_ARE_KEYS = 4, FXP_NORM_WHOLE = 8 };
 
+// One (token, head of q, k or v) by one warp. whole_q / whole_k: with FXP_NORM_WHOLE the factors 1 / rms of the token's
+// whole q and k projections (computed once per token by the caller), else unused.
 template <typename T>
-__global__ void __launch_bounds__(FX_WARPS * 32)
-attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ q_out, const float* __restrict__ q_gain,
-                         const float* __restrict__ k_gain, float eps, const float* __restrict__ freq, int rot,
-                         const int* __restrict__ positions, const int* __restrict__ req_index, const int* __restrict__ block_table,
-                         int bt_stride, int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages,
-                         int tokens, int heads, int kv_heads, int dk, int dv, int writes, int flags,
-                         const float* __restrict__ v_first, int ld_first, const float* __restrict__ vmix) {
-    pdl_launch_dependents();
-    pdl_wait();      // everything this kernel reads may come from the kernel before
-    __shared__ float x_s[FX_WARPS][FX_MAX_D];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int per_token = heads + 2 * kv_heads;
-    const long long wid = (long long)blockIdx.x * FX_WARPS + warp;
-    if (wid >= (long long)tokens * per_token) return;
-    const int t = (int)(wid / per_token), s = (int)(wid % per_token);
+__device__ __forceinline__ void prepare_unit(const float* __restrict__ qkv, int ld, T* __restrict__ q_out, const float* __restrict__ q_gain,
+                                             const float* __restrict__ k_gain, float eps, const float* __restrict__ freq, int rot,
+                                             const int* __restrict__ positions, const int* __restrict__ req_index,
+                                             const int* __restrict__ block_table, int bt_stride, int page_size, T* __restrict__ k_pages,
+                                             T* __restrict__ v_pages, int num_pages, int heads, int kv_heads, int dk, int dv, int writes, int flags,
+                                             const float* __restrict__ v_first, int ld_first, const float* __restrict__ vmix, int t, int s,
+                                             float whole_q, float whole_k, float* x_s, int lane) {
     const int pos = positions[t];
     const bool is_q = s < heads, is_k = !is_q && s < heads + kv_heads;
     const int head = is_q ? s : (is_k ? s - heads : s - heads - kv_heads);
@@ -72,19 +66,14 @@ attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ 
     const float* gain = is_q ? q_gain : k_gain;
     float norm = 1.0f;
     if (gain != nullptr && (flags & FXP_NORM_WHOLE)) {
-        // one root mean square over all heads of the projection; every warp of the token sums the row in the same order
-        const int n_all = (is_q ? heads : kv_heads) * dk;
-        const float* all = qkv + (size_t)t * ld + (is_q ? 0 : (size_t)heads * dk);
-        float ss = 0.f;
-        for (int c = lane; c < n_all; c += 32) ss = fmaf(all[c], all[c], ss);
-        norm = 1.0f / sqrtf(warp_sum(ss) / (float)n_all + eps);
+        norm = is_q ? whole_q : whole_k;
         gain += (size_t)head * dk;
     } else if (gain != nullptr) {
         float ss = 0.f;
         for (int c = lane; c < d; c += 32) ss = fmaf(src[c], src[c], ss);
         norm = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
     }
-    for (int c = lane; c < d; c += 32) x_s[warp][c] = gain != nullptr ? src[c] * norm * gain[c] : src[c];
+    for (int c = lane; c < d; c += 32) x_s[c] = gain != nullptr ? src[c] * norm * gain[c] : src[c];
     __syncwarp();
     const int half = rot >> 1;
     const bool interleaved = (flags & FXP_INTERLEAVED) != 0;
@@ -94,7 +83,7 @@ attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ 
     for (int j = 0; j < FX_MAX_D / 32; ++j) {
         const int c = lane + 32 * j;
         if (c >= d) break;
-        float v = x_s[warp][c];
+        float v = x_s[c];
         if (c < rot) {
             // the pair's first element is turned with minus, its second with plus; pairs are (i, i + rot/2) or (2i, 2i + 1)
             const bool first = interleaved ? (c & 1) == 0 : c < half;
@@ -102,7 +91,7 @@ attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ 
             const int mate = interleaved ? (c ^ 1) : (c < half ? c + half : c - half);
             const float a = (float)pos * freq[i];
             const float cs = cosf(a), sn = sinf(a);
-            v = first ? v * cs - x_s[warp][mate] * sn : v * cs + x_s[warp][mate] * sn;
+            v = first ? v * cs - x_s[mate] * sn : v * cs + x_s[mate] * sn;
         }
         y[j] = v;
         ss = fmaf(v, v, ss);
@@ -115,6 +104,51 @@ attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ 
         if (c >= d) break;
         Elem<T>::store(dst + c, y[j] * after);
     }
+    __syncwarp();       // x_s is the warp's own and may be filled again for its next unit
+}
+
+// Without FXP_NORM_WHOLE: a warp per (token, head of q, k or v), four of them a block. With it: a block per token, which
+// first sums the squares of the token's whole q and whole k (one fixed order of additions, whatever the batch), then its
+// warps take the token's heads in turn.
+template <typename T>
+__global__ void __launch_bounds__(FX_WARPS * 32)
+attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ q_out, const float* __restrict__ q_gain,
+                         const float* __restrict__ k_gain, float eps, const float* __restrict__ freq, int rot,
+                         const int* __restrict__ positions, const int* __restrict__ req_index, const int* __restrict__ block_table,
+                         int bt_stride, int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages,
+                         int tokens, int heads, int kv_heads, int dk, int dv, int writes, int flags,
+                         const float* __restrict__ v_first, int ld_first, const float* __restrict__ vmix) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
+    __shared__ float x_s[FX_WARPS][FX_MAX_D];
+    __shared__ float red[2][FX_WARPS];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (flags & FXP_NORM_WHOLE) {
+        const int t = blockIdx.x;
+        const float* row = qkv + (size_t)t * ld;
+        const int nq = heads * dk, nk = kv_heads * dk;
+        float sq = 0.f, sk = 0.f;
+        for (int c = threadIdx.x; c < nq; c += FX_WARPS * 32) sq = fmaf(row[c], row[c], sq);
+        for (int c = threadIdx.x; c < nk; c += FX_WARPS * 32) sk = fmaf(row[nq + c], row[nq + c], sk);
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        if (lane == 0) { red[0][warp] = sq; red[1][warp] = sk; }
+        __syncthreads();
+        sq = sk = 0.f;
+#pragma unroll
+        for (int w = 0; w < FX_WARPS; ++w) { sq += red[0][w]; sk += red[1][w]; }
+        const float whole_q = 1.0f / sqrtf(sq / (float)nq + eps), whole_k = 1.0f / sqrtf(sk / (float)nk + eps);
+        for (int s = warp; s < heads + 2 * kv_heads; s += FX_WARPS)
+            prepare_unit<T>(qkv, ld, q_out, q_gain, k_gain, eps, freq, rot, positions, req_index, block_table, bt_stride, page_size, k_pages, v_pages,
+                            num_pages, heads, kv_heads, dk, dv, writes, flags, v_first, ld_first, vmix, t, s, whole_q, whole_k, x_s[warp], lane);
+        return;
+    }
+    const int units = heads + 2 * kv_heads;
+    const long long wid = (long long)blockIdx.x * FX_WARPS + warp;
+    if (wid >= (long long)tokens * units) return;
+    prepare_unit<T>(qkv, ld, q_out, q_gain, k_gain, eps, freq, rot, positions, req_index, block_table, bt_stride, page_size, k_pages, v_pages,
+                    num_pages, heads, kv_heads, dk, dv, writes, flags, v_first, ld_first, vmix, (int)(wid / units), (int)(wid % units), 1.0f, 1.0f,
+                    x_s[warp], lane);
 }
 
 NIB_API int nib_attention_prepare(const float* qkv, int ld, void* q_out, const float* q_gain, const float* k_gain, float eps,
@@ -126,12 +160,13 @@ NIB_API int nib_attention_prepare(const float* qkv, int ld, void* q_out, const f
     NIB_REQUIRE(dk > 0 && dk <= FX_MAX_D && dv > 0 && dv <= FX_MAX_D, "attention_prepare: head sizes %d / %d are outside 1..%d", dk, dv, FX_MAX_D);
     NIB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dk && (rot == 0 || freq != nullptr), "attention_prepare: bad rotated width %d", rot);
     NIB_REQUIRE((q_gain == nullptr) == (k_gain == nullptr), "attention_prepare: q and k are normed together or not at all");
+    NIB_REQUIRE(!(flags & FXP_NORM_WHOLE) || q_gain != nullptr, "attention_prepare: a norm over the whole projection needs its gains");
     NIB_REQUIRE(!(flags & FXP_VALUES_ARE_KEYS) || dk == dv, "attention_prepare: values that are the keys have the keys' width");
     NIB_REQUIRE(!writes || (page_size > 0 && num_pages > 0 && block_table != nullptr), "attention_prepare: bad pages");
     NIB_REQUIRE(v_first == nullptr || (vmix != nullptr && ld_first >= kv_heads * dv && !(flags & FXP_VALUES_ARE_KEYS)),
                 "attention_prepare: a blend of values needs its factor and rows of at least kv_heads * dv floats");
     if (tokens == 0) return 0;
-    const dim3 grid(ceil_div((long long)tokens * (heads + 2 * kv_heads), FX_WARPS)), block(FX_WARPS * 32);
+    const dim3 grid((flags & FXP_NORM_WHOLE) ? tokens : ceil_div((long long)tokens * (heads + 2 * kv_heads), FX_WARPS)), block(FX_WARPS * 32);
     if (dtype == NIB_F32)
         NIB_CUDA(launch_pdl(attention_prepare_kernel<float>, grid, block, (size_t)0, stream, qkv, ld, (float*)q_out, q_gain, k_gain, eps, freq, rot,
                             positions, req_index, block_table, bt_stride, page_size, (float*)k_pages, (float*)v_pages, num_pages, tokens, heads,

@@ -20,6 +20,12 @@
 // softmax and output. Every wait is bounded; a wait that runs out records an error word, the CTA stops,
 // drains its copies, frees its TMEM and returns.
 //
+// A second instance of the kernel (FLEX) takes the options that other designs put on the scores: a soft cap
+// c tanh(s / c) (monotone, so the row's maximum is still the cap of the largest raw score; applied to every score in
+// 32-bit with the fast exponential and division before the exponent of the softmax), a chunked mask (a position sees its
+// own block of `chunk` positions, counted from the request's start), and a sink per head (exp(sink) once more in the
+// denominator, added where the row is divided by its sum). The instance without options is compiled without any of it.
+//
 // Formula as in attention_generic.cu (cpp/src/ops.cpp:206-270); the reference's prefill attention is a
 // SIMT kernel with 32-key shared-memory slabs (cpp/src/cuda/cuda_backend.cu:489-575).
 #include "tcgen05.cuh"
@@ -81,13 +87,14 @@ template <int HD> struct Cfg {
 constexpr float RESCALE_ABOVE = 8.0f;
 
 // grid: (row tiles, requests, kv heads)
-template <int HD>
+template <int HD, bool FLEX>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ q_start, const int* __restrict__ ctx_lens,
                             const int* __restrict__ block_table, int bt_stride, int page_size, int num_pages,
-                            int heads, int kv_heads, float scale, int window, unsigned long long* trace, int trace_cap) {
+                            int heads, int kv_heads, float scale, int window, unsigned long long* trace, int trace_cap,
+                            float softcap, int chunk, const float* __restrict__ sinks) {
     using C = Cfg<HD>;
     constexpr int KEYS = C::KEYS, STAGES = C::STAGES;
     extern __shared__ unsigned char smem_raw[];
@@ -121,7 +128,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int ctx = ctx_lens[req];
     const int pos0 = ctx - q_len + tok0;                  // position of the tile's first token
     const int hi_cta = pos0 + n_tok - 1;
-    const int lo_cta = window > 0 ? max(0, pos0 - window + 1) : 0;
+    int lo_cta = window > 0 ? max(0, pos0 - window + 1) : 0;
+    if (FLEX && chunk > 0) lo_cta = max(lo_cta, (pos0 / chunk) * chunk);      // (the first visible key never decreases with the position)
     const int b_begin = lo_cta / KEYS, n_blk = hi_cta / KEYS - b_begin + 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* bt = block_table + (size_t)req * bt_stride;
@@ -284,8 +292,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const bool live = row < n_tok * n_rep;
         const int ti = min(row / n_rep, n_tok - 1), head = kvh * n_rep + (row % n_rep);
         const int hi = pos0 + ti;
-        const int lo = window > 0 ? max(0, hi - window + 1) : 0;
-        const float scale2 = scale * LOG2E;
+        int lo = window > 0 ? max(0, hi - window + 1) : 0;
+        if (FLEX && chunk > 0) lo = max(lo, (hi / chunk) * chunk);
+        const bool capped = FLEX && softcap > 0.f;
+        // capped scores are turned into base-2 units where they are read, so the factor on them afterwards is one
+        const float scale2 = capped ? 1.0f : scale * LOG2E;
+        const float cap_in = capped ? 2.0f * scale / softcap : 0.f, cap_out = softcap * LOG2E;
         float m_cur = -INFINITY, l_run = 0.f;       // the maximum that the exponents refer to, and this thread's part of the sum
         bool ok = true;
         for (int j = 0; j < n_blk && ok; ++j) {
@@ -304,6 +316,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
             for (int c = 0; c < HK / 32; ++c) tmem_ld32_async(s_addr + c * 32, raw[c]);
             tmem_wait_ld();
+            if (capped) {
+                // c tanh(x / c) = c (1 - 2 / (1 + e^(2x/c))), off by a few 1e-7 in absolute terms
+#pragma unroll
+                for (int c = 0; c < HK / 32; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        raw[c][i] = __float_as_uint(cap_out * (1.0f - __fdividef(2.0f, 1.0f + __expf(cap_in * __uint_as_float(raw[c][i])))));
+            }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int c = 0; c < HK / 32; ++c) {
@@ -402,7 +422,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (lane == 0 && !s_failed) { atomicCAS(&g_attn_error, 0, (4 << 16) | (int)(blockIdx.x & 0xffff)); s_failed = 1; }
         } else {
             tc_fence_after();
-            const float l_all = xch[4 * 128 + row] + xch[5 * 128 + row];
+            float l_all = xch[4 * 128 + row] + xch[5 * 128 + row];
+            if (FLEX && sinks != nullptr && m_cur != -INFINITY) l_all += ex2(__ldg(sinks + head) * LOG2E - m_cur);   // the sink: no key, no value
             const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
             __nv_bfloat16* orow = out + ((size_t)(row_begin + tok0 + ti) * heads + head) * HD + half * (HD / 2);
 #pragma unroll
@@ -450,20 +471,21 @@ int make_map3(CUtensorMap* map, const void* ptr, long long d0, long long d1, lon
     return 0;
 }
 
-template <int HD>
+template <int HD, bool FLEX>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* q_start,
            const int* ctx_lens, const int* block_table, int bt_stride, int page_size, int num_pages, int n_req,
-           int max_q_len, int heads, int kv_heads, float scale, int window, cudaStream_t stream) {
+           int max_q_len, int heads, int kv_heads, float scale, int window, float softcap, int chunk, const float* sinks,
+           cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        NIB_CUDA(cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<HD>::SMEM));
+        NIB_CUDA(cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, FLEX>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<HD>::SMEM));
         configured = true;
     }
     const int tpt = ROWS / (heads / kv_heads);
     dim3 grid(ceil_div(max_q_len, tpt), n_req, kv_heads);
-    NIB_CUDA(launch_pdl(attention_prefill_tc_kernel<HD>, grid, dim3(THREADS), (size_t)Cfg<HD>::SMEM, stream, mq, mk, mv,
+    NIB_CUDA(launch_pdl(attention_prefill_tc_kernel<HD, FLEX>, grid, dim3(THREADS), (size_t)Cfg<HD>::SMEM, stream, mq, mk, mv,
                         (__nv_bfloat16*)out, q_start, ctx_lens, block_table, bt_stride, page_size, num_pages, heads,
-                        kv_heads, scale, window, nib_trace_buffer(), nib_trace_capacity()));
+                        kv_heads, scale, window, nib_trace_buffer(), nib_trace_capacity(), softcap, chunk, sinks));
     return 0;
 }
 
@@ -488,15 +510,17 @@ NIB_API int nib_attention_tc_error() {
     return v;
 }
 
-// Same arguments as nib_attention_prefill_mma plus the number of rows of qkv (m_tokens, for the map's extent).
+// Same arguments as nib_attention_prefill_mma plus the number of rows of qkv (m_tokens, for the map's extent), and the
+// options on the scores: softcap (0 = none), chunk (0 = none), sinks [heads] (null = none).
 NIB_API int nib_attention_prefill_tc(const void* qkv, int q_stride, void* out, const int* q_start, const int* ctx_lens,
                                      const int* block_table, int bt_stride, int page_size, const void* k_pages,
                                      const void* v_pages, int num_pages, int n_req, int max_q_len, int m_tokens,
-                                     int heads, int kv_heads, int head_dim, float scale, int window,
-                                     cudaStream_t stream) {
+                                     int heads, int kv_heads, int head_dim, float scale, int window, float softcap, int chunk,
+                                     const float* sinks, cudaStream_t stream) {
     NIB_REQUIRE(nib_attention_prefill_tc_supported(heads, kv_heads, head_dim, page_size, q_stride),
                 "attention (tcgen05): head_dim %d, %d/%d heads, page size %d are not supported", head_dim, heads, kv_heads, page_size);
-    NIB_REQUIRE(n_req >= 0 && max_q_len > 0 && num_pages > 0 && window >= 0 && m_tokens > 0, "attention (tcgen05): bad sizes");
+    NIB_REQUIRE(n_req >= 0 && max_q_len > 0 && num_pages > 0 && window >= 0 && m_tokens > 0 && chunk >= 0 && softcap >= 0.f && scale > 0.f,
+                "attention (tcgen05): bad sizes");
     NIB_REQUIRE((((uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) == 0, "attention (tcgen05): bases must be 16-byte aligned");
     NIB_REQUIRE(n_req <= 65535 && kv_heads <= 65535, "attention (tcgen05): too many requests or kv heads for one launch");
     if (n_req == 0) return 0;
@@ -508,9 +532,10 @@ NIB_API int nib_attention_prefill_tc(const void* qkv, int q_stride, void* out, c
     const long long planes = (long long)num_pages * kv_heads;
     if (make_map3(&mk, k_pages, head_dim, page_size, planes, head_dim, (long long)page_size * head_dim, page_size, 1)) return 1;
     if (make_map3(&mv, v_pages, head_dim, page_size, planes, head_dim, (long long)page_size * head_dim, page_size, 1)) return 1;
-    if (head_dim == 64)
-        return launch<64>(mq, mk, mv, out, q_start, ctx_lens, block_table, bt_stride, page_size, num_pages, n_req, max_q_len,
-                          heads, kv_heads, scale, window, stream);
-    return launch<128>(mq, mk, mv, out, q_start, ctx_lens, block_table, bt_stride, page_size, num_pages, n_req, max_q_len,
-                       heads, kv_heads, scale, window, stream);
+#define NIB_TC_ATTN(HD, FLEX) launch<HD, FLEX>(mq, mk, mv, out, q_start, ctx_lens, block_table, bt_stride, page_size, num_pages, n_req, max_q_len, \
+                                               heads, kv_heads, scale, window, softcap, chunk, sinks, stream)
+    const bool flex = softcap > 0.f || chunk > 0 || sinks != nullptr;
+    if (head_dim == 64) return flex ? NIB_TC_ATTN(64, true) : NIB_TC_ATTN(64, false);
+    return flex ? NIB_TC_ATTN(128, true) : NIB_TC_ATTN(128, false);
+#undef NIB_TC_ATTN
 }

@@ -511,7 +511,7 @@ class Kernels:
                 self._check(self._lib.nib_attention_prefill_tc(
                     _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), q_start, lens, table, c_int(bt_stride), c_int(page_size),
                     _ptr(k_pages), _ptr(v_pages), c_int(num_pages), c_int(n_req - n_dec), c_int(max(q_lens[n_dec:])),
-                    c_int(m), c_int(heads), c_int(kv_heads), c_int(head_dim), c_float(scale), c_int(window),
+                    c_int(m), c_int(heads), c_int(kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_float(0.0), c_int(0), None,
                     self._stream()), "attention prefill (tcgen05)")
             else:
                 self._check(self._lib.nib_attention_prefill_mma(
@@ -1082,6 +1082,17 @@ class Kernels:
             _need(sinks32, torch.float32, "attention sinks")
             if sinks32.numel() != heads:
                 raise KernelError("attention_flex: one sink per head")
+        n_rep = heads // max(1, kv_heads)
+        if q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and dim == vdim and slopes32 is None and out_scale == 1.0 \
+                and max(ctx.host.q_lens) * n_rep > 64 and not self.options.force_general_attention and not self.options.force_mma_prefill \
+                and self._lib.nib_attention_prefill_tc_supported(c_int(heads), c_int(kv_heads), c_int(dim), c_int(page_size), c_int(q.stride(0))) == 1:
+            # prompt portions with heads of 64 or 128 (keys and values alike): the tcgen05 kernel's instance with options
+            self._check(self._lib.nib_attention_prefill_tc(
+                _ptr(q), c_int(q.stride(0)), _ptr(out), _ptr(ctx.q_start), _ptr(ctx.ctx_lens), _ptr(block_table), c_int(block_table.stride(0)),
+                c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(k_pages.shape[0]), c_int(ctx.host.num_requests), c_int(max(ctx.host.q_lens)),
+                c_int(m), c_int(heads), c_int(kv_heads), c_int(dim), c_float(scale), c_int(window), c_float(softcap), c_int(chunk), _ptr(sinks32),
+                self._stream()), "attention (options, tcgen05)")
+            return
         if q.dtype == torch.bfloat16 and not self.options.force_general_attention and page_size > 0 \
                 and self._lib.nib_attention_flex_mma_supported(c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(q.stride(0))) == 1:
             # bfloat16 heads of up to 128 (multiples of 8): tensor cores, prompt portions and decoded tokens alike

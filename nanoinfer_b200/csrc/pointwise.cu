@@ -556,13 +556,24 @@ rmsnorm_add_kernel(float* __restrict__ y, const float* __restrict__ gain, float*
     }
     const float scale = mult / sqrtf(ss / (float)width + eps);
     if (next_gain != nullptr) {
-        // the sum, the sum of squares of the new row, and then the next norm of it
+        // the sum, the sum of squares of the new row, and then the next norm of it (the row comes back from L1/L2)
         float s2 = 0.f;
-        for (int c = first; c < width; c += step) {
-            const float v = xr[c] + yr[c] * scale * gain[c];
-            xr[c] = v;
-            s2 = fmaf(v, v, s2);
-            if (clear) yr[c] = 0.f;
+        if (vec) {
+            for (int c = first * 4; c < width; c += step * 4) {
+                const float4 yv = *reinterpret_cast<const float4*>(yr + c), g = __ldg(reinterpret_cast<const float4*>(gain + c));
+                float4 v = *reinterpret_cast<const float4*>(xr + c);
+                v.x += yv.x * scale * g.x; v.y += yv.y * scale * g.y; v.z += yv.z * scale * g.z; v.w += yv.w * scale * g.w;
+                *reinterpret_cast<float4*>(xr + c) = v;
+                s2 = fmaf(v.x, v.x, s2); s2 = fmaf(v.y, v.y, s2); s2 = fmaf(v.z, v.z, s2); s2 = fmaf(v.w, v.w, s2);
+                if (clear) *reinterpret_cast<float4*>(yr + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        } else {
+            for (int c = first; c < width; c += step) {
+                const float v = xr[c] + yr[c] * scale * gain[c];
+                xr[c] = v;
+                s2 = fmaf(v, v, s2);
+                if (clear) yr[c] = 0.f;
+            }
         }
         s2 = warp_sum(s2);
         if (BLOCK_ROW) {
@@ -573,8 +584,26 @@ rmsnorm_add_kernel(float* __restrict__ y, const float* __restrict__ gain, float*
             for (int w = 0; w < THREADS / 32; ++w) s2 += part[w];
         }
         const float scale2 = 1.0f / sqrtf(s2 / (float)width + next_eps);
-        if (h_out != nullptr)
+        if (h_out == nullptr) return;
+        if (vec) {      // (every thread reads back what it wrote itself)
+            for (int c = first * 4; c < width; c += step * 4) {
+                const float4 g = __ldg(reinterpret_cast<const float4*>(next_gain + c));
+                float4 v = *reinterpret_cast<const float4*>(xr + c);
+                v.x *= scale2 * g.x; v.y *= scale2 * g.y; v.z *= scale2 * g.z; v.w *= scale2 * g.w;
+                T* ho = h_out + (size_t)row * width + c;
+                if constexpr (sizeof(T) == 4) {
+                    *reinterpret_cast<float4*>(ho) = v;
+                } else {
+                    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<const unsigned*>(&lo);
+                    pk.y = *reinterpret_cast<const unsigned*>(&hi);
+                    *reinterpret_cast<uint2*>(ho) = pk;
+                }
+            }
+        } else {
             for (int c = first; c < width; c += step) Elem<T>::store(h_out + (size_t)row * width + c, xr[c] * scale2 * next_gain[c]);
+        }
         return;
     }
     if (vec) {
@@ -613,7 +642,7 @@ NIB_API int nib_rmsnorm_add(float* y, const float* gain, float* x, void* h_out, 
     NIB_REQUIRE(dtype == NIB_F32 || dtype == NIB_BF16, "rmsnorm_add: unknown dtype %d", dtype);
     if (rows == 0) return 0;
     const bool block_row = rows <= 64 && width >= 512;
-    const int vec = (width % 4 == 0 && (((uintptr_t)y | (uintptr_t)gain | (uintptr_t)x | (uintptr_t)h_out) & 15) == 0) ? 1 : 0;
+    const int vec = (width % 4 == 0 && (((uintptr_t)y | (uintptr_t)gain | (uintptr_t)x | (uintptr_t)h_out | (uintptr_t)next_gain) & 15) == 0) ? 1 : 0;
 #define NIB_RA(T, THREADS, GRID) \
     NIB_CUDA(launch_pdl(rmsnorm_add_kernel<T, THREADS>, dim3(GRID), dim3(THREADS), (size_t)0, stream, y, gain, x, (T*)h_out, rows, width, eps, mult, clear, vec, next_gain, next_eps))
     if (block_row) {

@@ -94,3 +94,20 @@ def test_the_designs_bench_sizes_are_configurations_the_registry_takes():
         assert readers and all(dar["layers"][dar["layers"][i]["mixer"]["kv_from"]]["type"] == "latent_attention" for i in readers)
         mlp = dar["layers"][0]["mlp"]
         assert mlp["router"]["top"] * mlp["expert"]["ff"] == size["ff_swiglu"]
+
+
+def test_the_fifth_designs_bench_sizes_are_configurations_the_registry_takes():
+    """``--design dusilorn``: both models of a size are valid configurations of equal width, depth and vocabulary; windowed and
+    chunked layers by turns; a token passes through as many feed-forward parameters in both (two experts and the shared one,
+    two matrices each and half as wide, against three matrices)."""
+    from nanoinfer_b200.registry import config_from_json_dict, plan_for
+    for size in bench.DUSILORN_SIZES.values():
+        dus, dense = bench.dusilorn_configs(size)
+        plan, dense_plan = plan_for(config_from_json_dict(dus)), plan_for(config_from_json_dict(dense))
+        assert len(plan.layers) == len(dense_plan.layers) == size["layers"]
+        assert plan.hidden_size == dense_plan.hidden_size == size["width"] and plan.vocab_size == dense_plan.vocab_size
+        kinds = [layer["type"] for layer in dus["layers"]]
+        assert kinds.count("attention") == kinds.count("attention_2") == size["layers"] // 2
+        mlp = dus["layers"][1]["mlp"]
+        assert 2 * (mlp["router"]["top"] * mlp["expert"]["ff"] + mlp["shared"]["ff"]) == 3 * size["ff_swiglu"]
+        assert dus["layers"][0]["mlp"]["kind"] == "dense" and plan.layers[1].parts["mixer"].params["v_mix"] == "blend"

@@ -242,7 +242,9 @@ def filled_pages(dtype, ctx_lens, bt, num_pages, kv, dim, vdim, page, seed):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv,dim,vdim,window,chunk,page,q_lens,before", [
     (4, 2, 12, 6, 0, 3, 4, [5, 1, 9], [3, 17, 0]), (8, 2, 64, 48, 0, 64, 16, [70, 1, 1], [130, 200, 63]), (8, 2, 96, 48, 136, 0, 16, [1, 1, 40], [300, 135, 120]),
-    (3, 1, 16, 24, 0, 17, 8, [33, 2], [0, 40]), (2, 2, 128, 128, 0, 100, 16, [1, 1, 1, 1], [99, 100, 450, 0]), (6, 3, 40, 8, 9, 0, 4, [12, 1], [4, 30])])
+    (3, 1, 16, 24, 0, 17, 8, [33, 2], [0, 40]), (2, 2, 128, 128, 0, 100, 16, [1, 1, 1, 1], [99, 100, 450, 0]), (6, 3, 40, 8, 9, 0, 4, [12, 1], [4, 30]),
+    (8, 2, 64, 64, 0, 64, 16, [70, 1, 130], [130, 200, 63]), (4, 2, 128, 128, 136, 0, 16, [200, 3], [100, 0]), (16, 2, 64, 64, 100, 0, 64, [300], [17]),
+    (4, 4, 128, 128, 0, 1000, 32, [129, 65], [0, 700])])
 def test_attention_with_a_sink_beside_chunks_and_windows(ops, dtype, heads, kv, dim, vdim, window, chunk, page, q_lens, before):
     """The kernels (tensor cores for bfloat16, one token per request with keys split over CTAs included) against the plain
     statement: capped scores, chunked or windowed mask by absolute position, exp(sink) once in the denominator."""
@@ -257,6 +259,12 @@ def test_attention_with_a_sink_beside_chunks_and_windows(ops, dtype, heads, kv, 
     TorchOps().attention_flex(q.cpu(), ref, heads, kv, dim, vdim, dim ** -0.5, 20.0, None, window, chunk, 1.0, to_cpu(ctx), bt.cpu(), page,
                               kp.cpu(), vp.cpu(), sinks32=sinks.cpu())
     assert_close(out, ref, dtype, "attention with a sink")
+    if dtype == torch.bfloat16:
+        # output in the storage type: prompt portions with heads of 64 or 128 take the kernel with scores in tensor memory
+        out_b = torch.empty(m, heads * vdim, dtype=dtype, device=DEV)
+        ops.attention_flex(q, out_b, heads, kv, dim, vdim, dim ** -0.5, 20.0, None, window, chunk, 1.0, ctx, bt, page, kp, vp, sinks32=sinks)
+        assert_close(out_b, ref, dtype, "attention with a sink, output in the storage type")
+        assert ops.gemm_tc_error() == 0 and ops.attention_tc_error() == 0
     no_sink = torch.empty_like(out)
     ops.attention_flex(q, no_sink, heads, kv, dim, vdim, dim ** -0.5, 20.0, None, window, chunk, 1.0, ctx, bt, page, kp, vp)
     assert (no_sink - out).abs().max().item() > 1e-3
@@ -297,6 +305,38 @@ def test_keys_just_inside_and_just_outside_an_edge_with_a_sink(ops, kind, size, 
         out = torch.empty(len(rows), dim, device=DEV)
         ops.attention_flex(q_all[rows].contiguous(), out, 1, 1, dim, dim, 1.0, 0.0, None, window, chunk, 1.0, ctx, bt, page, kp, vp, sinks32=sink)
         assert abs(out[-1, 2].item() - want) < 3e-2, (p, sees, out[-1, :4].tolist(), want)
+
+
+@pytest.mark.parametrize("kind,size,page", [("chunk", 64, 16), ("chunk", 100, 16), ("chunk", 128, 64), ("window", 64, 16), ("window", 136, 16), ("window", 257, 64)])
+def test_prompt_portions_with_scores_in_tensor_memory_see_the_same_edges(ops, kind, size, page):
+    """Heads of 64 in bfloat16, portions of 80 tokens that end just inside and just outside the edge: the marked key's
+    weight beside the sink, as above, on the tcgen05 path (and the same from the mma.sync path when it is pinned)."""
+    dim, n = 64, 2 * size + 150
+    a = (n // 2 // size) * size + size - 2 if kind == "chunk" else 37
+    qkv = torch.zeros(n, 3 * dim, device=DEV)
+    qkv[:, dim] = 1.0
+    qkv[a, dim + 1] = 9.0
+    qkv[a, 2 * dim + 2] = 4.0
+    qkv[:, 1] = 1.0
+    ctx_all, bt, num_pages = batch([n], [0], page_size=page)
+    kp = torch.zeros(num_pages, 1, page, dim, dtype=torch.bfloat16, device=DEV)
+    vp = torch.zeros(num_pages, 1, page, dim, dtype=torch.bfloat16, device=DEV)
+    q_all = torch.empty(n, dim, dtype=torch.bfloat16, device=DEV)
+    ops.attention_prepare(qkv, q_all, 1, 1, dim, dim, None, None, 1e-6, None, 0, ctx_all, bt, page, kp, vp, True)
+    sink = torch.tensor([math.log(3.0)], device=DEV)
+    last = (a // size) * size + size - 1 if kind == "chunk" else a + size - 1
+    window, chunk = (0, size) if kind == "chunk" else (size, 0)
+    for o in (ops, ops.with_options(force_mma_prefill=True)):
+        for p in (last, last + 1):
+            sees = p == last
+            lo = (p // size) * size if kind == "chunk" else max(0, p - size + 1)
+            others = (p - lo + 1) - (1 if sees else 0)
+            want = 4.0 * math.exp(9.0) / (math.exp(9.0) + others + 3.0) if sees else 0.0
+            ctx, _, _ = batch([80], [p - 79], page_size=page)
+            out = torch.empty(80, dim, dtype=torch.bfloat16, device=DEV)
+            o.attention_flex(q_all[p - 79:p + 1].contiguous(), out, 1, 1, dim, dim, 1.0, 0.0, None, window, chunk, 1.0, ctx, bt, page, kp, vp, sinks32=sink)
+            assert abs(out[-1, 2].item() - want) < 3e-2, (p, sees, out[-1, :4].float().tolist(), want)
+    assert ops.attention_tc_error() == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
