@@ -692,21 +692,24 @@ class Kernels:
                                               c_float(next_eps), self._stream()), "rmsnorm_add")
 
     # ---- routed experts (moe.cu) ---------------------------------------------------------------------------
-    def moe_route(self, z32, top, sel_e, sel_w, score="sigmoid", renormalize=False, correction32=None):
+    def moe_route(self, z32, top, sel_e, sel_w, score="sigmoid", renormalize=False, correction32=None, always=0):
         """From the router logits z32 [tokens, experts]: sel_e [tokens, top] int32 = the experts with the largest logits (the
         first of equal ones), sel_w [tokens, top] = sigmoid of their logits. Options: ``score`` 'softmax' (over all the logits
         of a token); ``correction32`` [experts] is added to the scores for the choice alone; ``renormalize`` divides the chosen
-        scores by their sum + 1e-20. With an option z32 is overwritten by the scores."""
+        scores by their sum + 1e-20. With an option z32 is overwritten by the scores. ``always`` n: every token also uses the
+        first n of the stacked experts (the pieces of a shared expert), so a chosen router output o is written as expert
+        o + n; sel_e and sel_w are [tokens, top + n], the last n entries of a row being the experts 0..n-1, each weighted by
+        sigmoid of the logit that stands behind the router's in the token's row (z32 is then a view of a wider matrix)."""
         self._rows(z32, torch.float32, "moe_route z"); _need(sel_e, torch.int32, "moe_route experts"); _need(sel_w, torch.float32, "moe_route weights")
         m, experts = z32.shape
-        if tuple(sel_e.shape) != (m, top) or tuple(sel_w.shape) != (m, top):
+        if tuple(sel_e.shape) != (m, top + always) or tuple(sel_w.shape) != (m, top + always) or (always and z32.stride(0) <= experts):
             raise KernelError("moe_route: shapes do not fit")
         if correction32 is not None:
             _need(correction32, torch.float32, "moe_route correction")
             if correction32.numel() != experts:
                 raise KernelError("moe_route: one correction per router output")
         self._check(self._lib.nib_moe_route(_ptr(z32), c_int(z32.stride(0)), _ptr(sel_e), _ptr(sel_w), c_int(m), c_int(experts), c_int(top),
-                                            c_int(_moe_mode(score, renormalize)), _ptr(correction32), self._stream()), "moe_route")
+                                            c_int(_moe_mode(score, renormalize)), _ptr(correction32), c_int(always), self._stream()), "moe_route")
 
     def _moe_tc(self, h, w_gate_up, w_down) -> bool:
         """bfloat16 in widths of 8 takes the tensor-core products; everything else (32-bit, odd widths) the CUDA cores."""
@@ -724,20 +727,23 @@ class Kernels:
                                tiles=idx[2 * n:2 * n + 3 * max_tiles], n_tiles=idx[2 * n + 3 * max_tiles:], rows=None)
 
     def moe_step(self, h, w_router, top, w_gate_up, w_down, sel_e, sel_w, score="sigmoid", renormalize=False, correction32=None,
-                 n_real=None, extra=0, z_extra=None):
+                 n_real=None, extra=0, z_extra=None, always=0):
         """A step of few tokens: router logits (32-bit sums over the stored ``h``), the choice, the grouping and the rows
         in the experts' order in ONE launch. Fills sel_e and sel_w like ``moe_route`` (same options) and returns what
         ``moe_experts`` takes as ``plan``; None when the step is too large for one block (the caller then takes the separate
         steps). ``n_real``: the first so many router outputs are experts (the others get no rows to multiply). ``extra``: the
-        last so many rows of ``w_router`` are no router outputs; their logits go to ``z_extra`` [tokens, extra]."""
+        last so many rows of ``w_router`` are no router outputs; their logits go to ``z_extra`` [tokens, extra] (if given).
+        ``always``: as for ``moe_route`` (then ``extra`` is 1: that row's logit is the gate; ``n_real`` counts those experts too)."""
         _need(h, None, "moe_step h"); _need(w_router, h.dtype, "moe_step router")
         m, hidden = h.shape
         experts = w_router.shape[0] - extra
-        n_real = experts if n_real is None else n_real
-        if m == 0 or self.options.no_moe_step or top > experts or \
+        n_real = experts + always if n_real is None else n_real
+        if m == 0 or self.options.no_moe_step or top > experts or m * (top + always) * hidden > (1 << 20) or \
                 self._lib.nib_moe_step_supported(c_int(m), c_int(hidden), c_int(experts + extra), c_int(top)) != 1:
             return None
-        if extra:
+        if always and (extra != 1 or tuple(sel_e.shape) != (m, top + always)):
+            raise KernelError("moe_step: always-used experts need the gate's row behind the router's and entries of top + always a token")
+        if extra and z_extra is not None:
             _need(z_extra, torch.float32, "moe_step extra logits")
             if tuple(z_extra.shape) != (m, extra):
                 raise KernelError("moe_step: the extra logits are [tokens, extra]")
@@ -746,14 +752,14 @@ class Kernels:
             if correction32.numel() != experts:
                 raise KernelError("moe_step: one correction per router output")
         tc = self._moe_tc(h, w_gate_up, w_down)
-        plan = self._moe_tables(m * top, experts, tc, h.device)
+        plan = self._moe_tables(m * (top + always), experts + always, tc, h.device)
         if tc:
-            plan.rows = torch.empty((m * top, hidden), dtype=h.dtype, device=h.device)
+            plan.rows = torch.empty((m * (top + always), hidden), dtype=h.dtype, device=h.device)
         self._check(self._lib.nib_moe_step(_ptr(h), c_int(h.stride(0)), _ptr(w_router), c_int(m), c_int(hidden), c_int(experts), c_int(top),
                                            _ptr(sel_e), _ptr(sel_w), c_int(plan.tile_rows), _ptr(plan.row_of), _ptr(plan.src_of), _ptr(plan.tiles),
                                            _ptr(plan.n_tiles), c_int(plan.max_tiles), _ptr(plan.rows), c_int(_DT[h.dtype]),
                                            c_int(_moe_mode(score, renormalize)), _ptr(correction32), c_int(n_real), c_int(extra), _ptr(z_extra),
-                                           self._stream()), "experts: router, choice and grouping of a short step")
+                                           c_int(always), self._stream()), "experts: router, choice and grouping of a short step")
         return plan
 
     def moe_experts(self, h, sel_e, sel_w, w_gate_up, w_down, out32, plan=None, gated=True, weight_on="input", outputs=None):
@@ -812,33 +818,16 @@ class Kernels:
             self._check(self._lib.nib_moe_combine(_ptr(y), _ptr(p.row_of), _ptr(out32), c_int(m), c_int(hidden), c_int(top), self._stream()),
                         "experts: sum of a token's choices")
 
-    def moe_side(self, h, out32=None, sel_e=None, sel_w=None, n_real=0, u32=None, act=None, gate32=None, kind="relu2"):
-        """What stands beside routed experts, per token, in one launch; either half may be absent. Identity experts (with
-        ``sel_e``): out32[t] += (the sum of sel_w[t, c] over the choices with sel_e[t, c] >= n_real) * h[t]. The activation of
-        an expert that every token uses (with ``act``): act[t] = g * f(u32[t]) in h's type, f = relu(.)^2 (``kind`` 'relu2')
-        or the identity ('none'), g = sigmoid(gate32[t]) with one gate logit per token (a column, any row stride), else 1."""
-        _need(h, None, "moe_side h")
+    def moe_identity(self, h, out32, sel_e, sel_w, n_real):
+        """Identity outputs of a router: out32[t] += (the sum of sel_w[t, c] over the choices with sel_e[t, c] >= n_real) * h[t]."""
+        _need(h, None, "moe_identity h"); _need(sel_e, torch.int32, "moe_identity experts"); _need(sel_w, torch.float32, "moe_identity weights")
+        self._rows(out32, torch.float32, "moe_identity out")
         m, hidden = h.shape
-        top = ff = 0
-        if sel_e is not None:
-            _need(sel_e, torch.int32, "moe_side experts"); _need(sel_w, torch.float32, "moe_side weights"); self._rows(out32, torch.float32, "moe_side out")
-            top = sel_e.shape[1]
-            if tuple(sel_e.shape) != (m, top) or tuple(sel_w.shape) != (m, top) or tuple(out32.shape) != (m, hidden):
-                raise KernelError("moe_side: shapes do not fit")
-        if act is not None:
-            self._rows(u32, torch.float32, "moe_side u"); self._rows(act, h.dtype, "moe_side act")
-            ff = u32.shape[1]
-            if tuple(u32.shape) != (m, ff) or tuple(act.shape) != (m, ff):
-                raise KernelError("moe_side: shapes do not fit")
-            if gate32 is not None:
-                _need(gate32, torch.float32, "moe_side gate", contiguous=False)
-                if gate32.shape[0] != m or gate32.numel() != m:
-                    raise KernelError("moe_side: one gate logit per token")
-        self._check(self._lib.nib_moe_side(
-            _ptr(h), c_int(h.stride(0)), _ptr(sel_e), _ptr(sel_w), c_int(top), c_int(n_real), _ptr(out32), c_int(out32.stride(0) if out32 is not None else 0),
-            c_int(hidden), _ptr(u32), c_int(u32.stride(0) if u32 is not None else 0), _ptr(gate32), c_int(gate32.stride(0) if gate32 is not None else 0),
-            _ptr(act), c_int(act.stride(0) if act is not None else 0), c_int(ff), c_int({"none": 0, "relu2": 1}[kind]), c_int(m), c_int(_DT[h.dtype]),
-            self._stream()), "moe_side")
+        top = sel_e.shape[1]
+        if tuple(sel_e.shape) != (m, top) or tuple(sel_w.shape) != (m, top) or tuple(out32.shape) != (m, hidden):
+            raise KernelError("moe_identity: shapes do not fit")
+        self._check(self._lib.nib_moe_identity(_ptr(h), c_int(h.stride(0)), _ptr(sel_e), _ptr(sel_w), c_int(top), c_int(n_real), _ptr(out32),
+                                               c_int(out32.stride(0)), c_int(hidden), c_int(m), c_int(_DT[h.dtype]), self._stream()), "moe_identity")
 
     # ---- gate, norm in groups, skip (pointwise.cu) ---------------------------------------------------------
     def gated_norm(self, o32, out, groups=0, eps=0.0, gain32=None, gate32=None, gate_kind="none", gate_first=False,

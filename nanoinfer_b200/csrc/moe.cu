@@ -18,8 +18,12 @@
 //    the scores for the CHOICE only (`corr`); the chosen scores divided by their sum + 1e-20 (MOE_RENORM);
 //  * the weight on the expert's OUTPUT instead of its input (`w_out`);
 //  * experts without a gate: W_down relu(W_up x)^2 (mode 2 of the products);
-//  * router outputs from `n_real` on that stand for no expert (the caller adds what they mean, see moe_side in
-//    pointwise.cu): they are chosen and weighted like the others, but get no row tiles.
+//  * router outputs from `n_real` on that stand for no expert (the caller adds what they mean, see moe_identity in
+//    pointwise.cu): they are chosen and weighted like the others, but get no row tiles;
+//  * `always` experts that every token uses (a shared expert, cut into pieces of the experts' width): they are the first
+//    `always` of the stacked experts, so a chosen router output o becomes expert o + always; every token gets `always` more
+//    entries behind its `top` chosen ones, each weighted by sigmoid of one more logit that stands behind the router's in
+//    the token's row (zr[experts]). The entries of a token are then `top + always` wide.
 #include "common.cuh"
 #include <climits>
 
@@ -30,8 +34,13 @@ enum { MOE_SOFTMAX = 1, MOE_RENORM = 2 };
 // One warp chooses for one token: the `top` largest of zr[0..experts) (the first of equal ones) and their sigmoids.
 // With options the logits are first turned into scores IN PLACE (softmax over all of them, or sigmoid), the choice goes
 // by score + corr, and the weights are the chosen scores, divided by their sum + 1e-20 with MOE_RENORM.
-__device__ __forceinline__ void route_token(float* zr, int experts, int top, int lane, int* sel_e, float* sel_w, int mode, const float* corr) {
+__device__ __forceinline__ void route_token(float* zr, int experts, int top, int lane, int* sel_e, float* sel_w, int mode, const float* corr,
+                                            int always) {
     unsigned taken = 0;     // bit j: this lane's expert lane + 32 j is chosen already
+    if (always > 0 && lane == 0) {
+        const float g = 1.0f / (1.0f + expf(-zr[experts]));
+        for (int j = 0; j < always; ++j) { sel_e[top + j] = j; sel_w[top + j] = g; }
+    }
     if (mode != 0 || corr != nullptr) {
         if (mode & MOE_SOFTMAX) {
             float mx = -INFINITY;
@@ -64,7 +73,7 @@ __device__ __forceinline__ void route_token(float* zr, int experts, int top, int
             if (bi == INT_MAX) bi = 0;
             if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
             if (lane == 0) {
-                sel_e[k] = bi;
+                sel_e[k] = bi + always;
                 sel_w[k] = zr[bi];
                 total += zr[bi];
             }
@@ -93,7 +102,7 @@ __device__ __forceinline__ void route_token(float* zr, int experts, int top, int
         if (bi == INT_MAX) bi = 0;
         if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
         if (lane == 0) {
-            sel_e[k] = bi;
+            sel_e[k] = bi + always;
             sel_w[k] = 1.0f / (1.0f + expf(-best));
         }
     }
@@ -101,12 +110,12 @@ __device__ __forceinline__ void route_token(float* zr, int experts, int top, int
 
 __global__ void __launch_bounds__(128)
 moe_route_kernel(float* __restrict__ z, int ldz, int* __restrict__ sel_e, float* __restrict__ sel_w, int tokens, int experts, int top, int mode,
-                 const float* __restrict__ corr) {
+                 const float* __restrict__ corr, int always) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
     const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= tokens) return;
-    route_token(z + (size_t)t * ldz, experts, top, lane, sel_e + (size_t)t * top, sel_w + (size_t)t * top, mode, corr);
+    route_token(z + (size_t)t * ldz, experts, top, lane, sel_e + (size_t)t * (top + always), sel_w + (size_t)t * (top + always), mode, corr, always);
 }
 
 // The (token, choice) entries ordered by expert, by one block of any size. tiles: [max_tiles, 3] = (expert, first row,
@@ -188,7 +197,7 @@ __global__ void __launch_bounds__(1024)
 moe_step_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ w_router, int tokens, int hidden, int experts, int top,
                 int* __restrict__ sel_e, float* __restrict__ sel_w, int tile_rows, int* __restrict__ row_of, int* __restrict__ src_of,
                 int* __restrict__ tiles, int* __restrict__ n_tiles, int max_tiles, T* __restrict__ rows, int vec, int mode,
-                const float* __restrict__ corr, int n_real, int extra, float* __restrict__ z_extra) {
+                const float* __restrict__ corr, int n_real, int extra, float* __restrict__ z_extra, int always) {
     constexpr int V = 16 / (int)sizeof(T);
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
@@ -217,13 +226,15 @@ moe_step_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ w_router
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
         if (lane == 0) {
             z[p] = acc;
-            if (e >= experts) z_extra[(size_t)t * extra + (e - experts)] = acc;
+            if (e >= experts && z_extra != nullptr) z_extra[(size_t)t * extra + (e - experts)] = acc;
         }
     }
     __syncthreads();
     for (int t = warp; t < tokens; t += warps)
-        route_token(z + t * outs, experts, top, lane, sel_e + (size_t)t * top, sel_w + (size_t)t * top, mode, corr);
+        route_token(z + t * outs, experts, top, lane, sel_e + (size_t)t * (top + always), sel_w + (size_t)t * (top + always), mode, corr, always);
     __syncthreads();        // the block's own writes to sel_e are visible to all of its threads
+    top += always;          // from here on a token's entries are its chosen and its always-used experts
+    experts += always;
     const int n = tokens * top;
     group_entries(sel_e, n, experts, tile_rows, row_of, src_of, tiles, n_tiles, max_tiles, cnt, off, toff, cur, n_real);
     if (rows == nullptr) return;
@@ -370,12 +381,13 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of, 
 }
 
 // mode: MOE_SOFTMAX | MOE_RENORM; corr: [experts] or null. With a mode or a correction z is overwritten by the scores.
+// always > 0: sel_e and sel_w are [tokens, top + always], z holds one more logit behind the router's (ldz > experts).
 NIB_API int nib_moe_route(float* z, int ldz, int* sel_e, float* sel_w, int tokens, int experts, int top, int mode, const float* corr,
-                          cudaStream_t stream) {
-    NIB_REQUIRE(tokens >= 0 && experts > 0 && experts <= MOE_MAX_EXPERTS && top > 0 && top <= experts,
-                "moe_route: %d experts (up to %d), %d chosen", experts, MOE_MAX_EXPERTS, top);
+                          int always, cudaStream_t stream) {
+    NIB_REQUIRE(tokens >= 0 && experts > 0 && experts + always <= MOE_MAX_EXPERTS && top > 0 && top <= experts && always >= 0 && (always == 0 || ldz > experts),
+                "moe_route: %d experts (up to %d), %d chosen, %d always", experts, MOE_MAX_EXPERTS, top, always);
     if (tokens == 0) return 0;
-    NIB_CUDA(launch_pdl(moe_route_kernel, dim3(ceil_div(tokens, 4)), dim3(128), (size_t)0, stream, z, ldz, sel_e, sel_w, tokens, experts, top, mode, corr));
+    NIB_CUDA(launch_pdl(moe_route_kernel, dim3(ceil_div(tokens, 4)), dim3(128), (size_t)0, stream, z, ldz, sel_e, sel_w, tokens, experts, top, mode, corr, always));
     NIB_LAUNCH_CHECK();
     return 0;
 }
@@ -408,20 +420,23 @@ NIB_API int nib_moe_step_supported(int tokens, int hidden, int experts, int top)
 // [experts, hidden] in the storage type; the other arguments as for moe_route and moe_group.
 NIB_API int nib_moe_step(const void* h, int ldh, const void* w_router, int tokens, int hidden, int experts, int top, int* sel_e, float* sel_w,
                          int tile_rows, int* row_of, int* src_of, int* tiles, int* n_tiles, int max_tiles, void* rows, int dtype, int mode,
-                         const float* corr, int n_real, int extra, float* z_extra, cudaStream_t stream) {
-    NIB_REQUIRE(extra >= 0 && nib_moe_step_supported(tokens, hidden, experts + extra, top) == 1 && top <= experts && ldh >= hidden && tile_rows > 0
-                && max_tiles >= nib_moe_max_tiles(tokens * top, experts, tile_rows) && n_real >= 0 && n_real <= experts
-                && (extra == 0 || z_extra != nullptr), "moe_step: bad sizes");
+                         const float* corr, int n_real, int extra, float* z_extra, int always, cudaStream_t stream) {
+    // (with `always`: n_real counts the always-used experts too; the tables are made for top + always entries a token)
+    NIB_REQUIRE(extra >= 0 && always >= 0 && nib_moe_step_supported(tokens, hidden, experts + extra, top) == 1 && top <= experts && ldh >= hidden
+                && (long long)tokens * (top + always) * hidden <= (1LL << 20)
+                && tile_rows > 0 && max_tiles >= nib_moe_max_tiles(tokens * (top + always), experts + always, tile_rows) && n_real >= 0
+                && n_real <= experts + always && experts + always <= MOE_MAX_EXPERTS && (always == 0 || extra == 1),
+                "moe_step: bad sizes");
     NIB_REQUIRE(dtype == NIB_F32 || dtype == NIB_BF16, "moe_step: unknown dtype %d", dtype);
     const int per16 = dtype == NIB_F32 ? 4 : 8;
     const int vec = (hidden % per16 == 0 && ldh % per16 == 0 && (((uintptr_t)h | (uintptr_t)w_router | (uintptr_t)rows) & 15) == 0) ? 1 : 0;
     if (dtype == NIB_F32)
         NIB_CUDA(launch_pdl(moe_step_kernel<float>, dim3(1), dim3(1024), (size_t)0, stream, (const float*)h, ldh, (const float*)w_router, tokens, hidden,
-                            experts, top, sel_e, sel_w, tile_rows, row_of, src_of, tiles, n_tiles, max_tiles, (float*)rows, vec, mode, corr, n_real, extra, z_extra));
+                            experts, top, sel_e, sel_w, tile_rows, row_of, src_of, tiles, n_tiles, max_tiles, (float*)rows, vec, mode, corr, n_real, extra, z_extra, always));
     else
         NIB_CUDA(launch_pdl(moe_step_kernel<__nv_bfloat16>, dim3(1), dim3(1024), (size_t)0, stream, (const __nv_bfloat16*)h, ldh,
                             (const __nv_bfloat16*)w_router, tokens, hidden, experts, top, sel_e, sel_w, tile_rows, row_of, src_of, tiles, n_tiles,
-                            max_tiles, (__nv_bfloat16*)rows, vec, mode, corr, n_real, extra, z_extra));
+                            max_tiles, (__nv_bfloat16*)rows, vec, mode, corr, n_real, extra, z_extra, always));
     NIB_LAUNCH_CHECK();
     return 0;
 }

@@ -655,51 +655,35 @@ NIB_API int nib_rmsnorm_add(float* y, const float* gain, float* x, void* h_out, 
     return 0;
 }
 
-// ---------------------------------------------------------------------------------- what stands beside routed experts
-// Two per-token steps of a mixture of experts, in one launch of a block per token; either may be absent.
-//  * identity experts: the router outputs from `n_real` on have no weights, their output is the token's input itself, so
-//    out[t] += (sum of the weights of the token's choices e >= n_real) * h[t].
-//  * the activation of an expert that every token uses: act[t, c] = g * relu(u[t, c])^2 (kind 1) or g * u (kind 0), with
-//    g = sigmoid(gate[t * ld_gate]) when a gate logit per token is given, else 1; u is 32-bit, act leaves in T.
+// ---------------------------------------------------------------------------------- identity outputs of a router
+// The router outputs from `n_real` on have no weights: such a choice stands for the token's input itself, so
+// out[t] += (sum of the weights of the token's choices e >= n_real) * h[t]. A block per token.
 template <typename T>
 __global__ void __launch_bounds__(256)
-moe_side_kernel(const T* __restrict__ h, int ldh, const int* __restrict__ sel_e, const float* __restrict__ sel_w, int top, int n_real,
-                float* __restrict__ out, int ldo, int hidden, const float* __restrict__ u, int ldu, const float* __restrict__ gate,
-                int ld_gate, T* __restrict__ act, int lda, int ff, int kind) {
+moe_identity_kernel(const T* __restrict__ h, int ldh, const int* __restrict__ sel_e, const float* __restrict__ sel_w, int top, int n_real,
+                    float* __restrict__ out, int ldo, int hidden) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
     const int t = blockIdx.x;
-    if (sel_e != nullptr) {
-        float wsum = 0.f;
-        bool any = false;
-        for (int k = 0; k < top; ++k)       // ascending order of choice, the same in every thread
-            if (sel_e[(size_t)t * top + k] >= n_real) { wsum += sel_w[(size_t)t * top + k]; any = true; }
-        if (any)
-            for (int c = threadIdx.x; c < hidden; c += 256) out[(size_t)t * ldo + c] += wsum * Elem<T>::load(h + (size_t)t * ldh + c);
-    }
-    if (act != nullptr) {
-        const float g = gate != nullptr ? 1.0f / (1.0f + expf(-gate[(size_t)t * ld_gate])) : 1.0f;
-        for (int c = threadIdx.x; c < ff; c += 256) {
-            float v = u[(size_t)t * ldu + c];
-            if (kind == 1) { v = fmaxf(v, 0.f); v = v * v; }
-            Elem<T>::store(act + (size_t)t * lda + c, g * v);
-        }
-    }
+    float wsum = 0.f;
+    bool any = false;
+    for (int k = 0; k < top; ++k)       // ascending order of choice, the same in every thread
+        if (sel_e[(size_t)t * top + k] >= n_real) { wsum += sel_w[(size_t)t * top + k]; any = true; }
+    if (!any) return;
+    for (int c = threadIdx.x; c < hidden; c += 256) out[(size_t)t * ldo + c] += wsum * Elem<T>::load(h + (size_t)t * ldh + c);
 }
 
-NIB_API int nib_moe_side(const void* h, int ldh, const int* sel_e, const float* sel_w, int top, int n_real, float* out, int ldo, int hidden,
-                         const float* u, int ldu, const float* gate, int ld_gate, void* act, int lda, int ff, int kind, int tokens, int dtype,
-                         cudaStream_t stream) {
-    NIB_REQUIRE(tokens >= 0 && (sel_e == nullptr || (sel_w != nullptr && out != nullptr && h != nullptr && top > 0 && hidden > 0)) &&
-                (act == nullptr || (u != nullptr && ff > 0 && kind >= 0 && kind <= 1)), "moe_side: bad arguments");
-    NIB_REQUIRE(dtype == NIB_F32 || dtype == NIB_BF16, "moe_side: unknown dtype %d", dtype);
-    if (tokens == 0 || (sel_e == nullptr && act == nullptr)) return 0;
+NIB_API int nib_moe_identity(const void* h, int ldh, const int* sel_e, const float* sel_w, int top, int n_real, float* out, int ldo, int hidden,
+                             int tokens, int dtype, cudaStream_t stream) {
+    NIB_REQUIRE(tokens >= 0 && sel_e != nullptr && sel_w != nullptr && out != nullptr && h != nullptr && top > 0 && hidden > 0 && n_real >= 0,
+                "moe_identity: bad arguments");
+    NIB_REQUIRE(dtype == NIB_F32 || dtype == NIB_BF16, "moe_identity: unknown dtype %d", dtype);
+    if (tokens == 0) return 0;
     if (dtype == NIB_F32)
-        NIB_CUDA(launch_pdl(moe_side_kernel<float>, dim3(tokens), dim3(256), (size_t)0, stream, (const float*)h, ldh, sel_e, sel_w, top, n_real, out, ldo,
-                            hidden, u, ldu, gate, ld_gate, (float*)act, lda, ff, kind));
+        NIB_CUDA(launch_pdl(moe_identity_kernel<float>, dim3(tokens), dim3(256), (size_t)0, stream, (const float*)h, ldh, sel_e, sel_w, top, n_real, out, ldo, hidden));
     else
-        NIB_CUDA(launch_pdl(moe_side_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), (size_t)0, stream, (const __nv_bfloat16*)h, ldh, sel_e, sel_w, top,
-                            n_real, out, ldo, hidden, u, ldu, gate, ld_gate, (__nv_bfloat16*)act, lda, ff, kind));
+        NIB_CUDA(launch_pdl(moe_identity_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), (size_t)0, stream, (const __nv_bfloat16*)h, ldh, sel_e, sel_w, top,
+                            n_real, out, ldo, hidden));
     NIB_LAUNCH_CHECK();
     return 0;
 }

@@ -99,7 +99,10 @@ class RoutedExperts(FeedForward):
       ``weight * h``;
     * ``shared`` ff: one more expert of the experts' form, ``ff`` wide, that every token uses; its result is multiplied by
       ``sigmoid(W_sg h)``, one number per token (tensors ``shared_up``, ``shared_down``, ``shared_sg [1, hidden]``; for
-      experts without a gate). Its gate logit is one more row of the router's product.
+      experts without a gate, whose inner channels do not meet before the down product: the shared expert is cut into
+      pieces of the experts' width (the last one filled up with zero rows, which add nothing) that stand FIRST in the
+      stacked matrices and that every token uses with the weight ``sigmoid(W_sg h)``, so it runs inside the same grouped
+      products as the chosen experts). Its gate logit is one more row of the router's product.
 
     params: ``hidden``, ``ff`` (an expert's inner width), ``experts``, ``top`` and the options. tensors: ``router [experts +
     identity, hidden]`` and per expert i ``e<i>_gate, e<i>_up [ff, hidden]``, ``e<i>_down [hidden, ff]``; they are stacked once at
@@ -150,20 +153,30 @@ class RoutedExperts(FeedForward):
         self.w_router = rt.matrix(torch.cat(rows, dim=0))
         self.correction = rt.vector32(tensors["correction"]) if p.get("correction") else None
         first = (lambda i: torch.cat([tensors[f"e{i}_gate"], tensors[f"e{i}_up"]], dim=0)) if self.gated else (lambda i: tensors[f"e{i}_up"])
-        self.w_gate_up = rt.matrix(torch.stack([first(i) for i in range(self.experts)]))
-        self.w_down = rt.matrix(torch.stack([tensors[f"e{i}_down"] for i in range(self.experts)]))
+        ups = [first(i) for i in range(self.experts)]
+        downs = [tensors[f"e{i}_down"] for i in range(self.experts)]
+        self.pieces = -(-self.shared // self.ff) if self.shared else 0     # the shared expert as experts of the common width
         if self.shared:
-            self.w_shared_up = rt.matrix(tensors["shared_up"])
-            self.w_shared_down = rt.matrix(tensors["shared_down"])
+            if self.weight_on != "output":
+                raise ValueError("a shared expert's gate multiplies its result: the weights of this mixture stand on the output")
+            up, down = tensors["shared_up"], tensors["shared_down"]
+            fill = self.pieces * self.ff - self.shared
+            if fill:
+                up = torch.cat([up, torch.zeros((fill, self.hidden), dtype=up.dtype)], dim=0)
+                down = torch.cat([down, torch.zeros((self.hidden, fill), dtype=down.dtype)], dim=1)
+            ups = [up[j * self.ff:(j + 1) * self.ff] for j in range(self.pieces)] + ups
+            downs = [down[:, j * self.ff:(j + 1) * self.ff] for j in range(self.pieces)] + downs
+        self.w_gate_up = rt.matrix(torch.stack(ups))
+        self.w_down = rt.matrix(torch.stack(downs))
         self.plain = self.score == "sigmoid" and not self.renormalize and self.correction is None and self.weight_on == "input" \
             and self.gated and not self.identity and not self.shared
 
     def forward(self, h, residual32: torch.Tensor, ctx: StepContext) -> None:
         h = as_tensor(h)
         m, dev = h.shape[0], h.device
-        chosen = torch.empty((m, self.top), dtype=torch.int32, device=dev)
-        weight = torch.empty((m, self.top), dtype=torch.float32, device=dev)
         if self.plain:
+            chosen = torch.empty((m, self.top), dtype=torch.int32, device=dev)
+            weight = torch.empty((m, self.top), dtype=torch.float32, device=dev)
             # a short step (decoding): router, choice and grouping are one launch where the backend has one
             step = getattr(self.ops, "moe_step", None)
             plan = step(h, self.w_router, self.top, self.w_gate_up, self.w_down, chosen, weight) if step is not None else None
@@ -175,33 +188,21 @@ class RoutedExperts(FeedForward):
             self.ops.moe_route(z32, self.top, chosen, weight)
             self.ops.moe_experts(h, chosen, weight, self.w_gate_up, self.w_down, residual32)
             return
-        extra = 1 if self.shared else 0
-        options = dict(score=self.score, renormalize=self.renormalize, correction32=self.correction)
+        extra, always = (1, self.pieces) if self.shared else (0, 0)
+        chosen = torch.empty((m, self.top + always), dtype=torch.int32, device=dev)
+        weight = torch.empty((m, self.top + always), dtype=torch.float32, device=dev)
+        options = dict(score=self.score, renormalize=self.renormalize, correction32=self.correction, always=always)
         step = getattr(self.ops, "moe_step", None)
-        gate32 = torch.empty((m, extra), dtype=torch.float32, device=dev) if extra else None
-        plan = step(h, self.w_router, self.top, self.w_gate_up, self.w_down, chosen, weight, n_real=self.experts, extra=extra,
-                    z_extra=gate32, **options) if step is not None else None
+        plan = step(h, self.w_router, self.top, self.w_gate_up, self.w_down, chosen, weight, n_real=self.experts + always, extra=extra,
+                    **options) if step is not None else None
         if plan is None:
             z32 = torch.empty((m, self.outputs + extra), dtype=torch.float32, device=dev)
             self.ops.linear(h, self.w_router, None, z32, "f32")
             self.ops.moe_route(z32[:, :self.outputs], self.top, chosen, weight, **options)
-            gate32 = z32[:, self.outputs:] if extra else None
         self.ops.moe_experts(h, chosen, weight, self.w_gate_up, self.w_down, residual32, plan=plan, gated=self.gated,
-                             weight_on=self.weight_on, outputs=self.outputs)
-        if not self.shared:
-            if self.identity:
-                self.ops.moe_side(h, residual32, chosen, weight, self.experts)
-            return
-        # the expert that every token uses: its first product, then (one launch) its activation times the token's gate and the
-        # identity choices' share, then its down product into the stream
-        act = torch.empty((m, self.shared), dtype=self.rt.dtype, device=dev)
-        u32 = torch.empty((m, self.shared), dtype=torch.float32, device=dev)
-        self.ops.linear(h, self.w_shared_up, None, u32, "f32")
+                             weight_on=self.weight_on, outputs=self.outputs + always)
         if self.identity:
-            self.ops.moe_side(h, residual32, chosen, weight, self.experts, u32=u32, act=act, gate32=gate32, kind="relu2")
-        else:
-            self.ops.moe_side(h, u32=u32, act=act, gate32=gate32, kind="relu2")
-        self.ops.linear(act, self.w_shared_down, None, residual32, "add")
+            self.ops.moe_identity(h, residual32, chosen, weight, self.experts + always)
 
 
 register_part("routed_experts", RoutedExperts)

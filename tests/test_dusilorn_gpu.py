@@ -147,7 +147,7 @@ def test_experts_without_a_gate_weighted_on_the_output_with_identity_outputs(ops
         out = before.clone()
         o.moe_experts(h, sel_e, sel_w, up, down, out, gated=False, weight_on="output", outputs=outputs)
         if identity:
-            o.moe_side(h, out, sel_e, sel_w, experts)
+            o.moe_identity(h, out, sel_e, sel_w, experts)
         assert_close(out - before, ref, dtype, "mixture " + name)
 
 
@@ -180,20 +180,59 @@ def test_a_short_step_with_the_router_options_in_one_launch(ops, dtype, m, hidde
     before = rnd(m, hidden, seed=3)
     out = before.clone()
     ops.moe_experts(h, sel_e, sel_w, up, down, out, plan=plan, gated=False, weight_on="output", outputs=outputs)
-    ops.moe_side(h, out, sel_e, sel_w, experts)
+    ops.moe_identity(h, out, sel_e, sel_w, experts)
     assert_close(out - before, plain.mixture(mlp, wd, "r", h.double().cpu()), dtype, "mixture of a short step")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("m,hidden,ff", [(1, 16, 8), (9, 72, 40), (130, 128, 300)])
-def test_the_shared_experts_activation_takes_the_tokens_gate(ops, dtype, m, hidden, ff):
+@pytest.mark.parametrize("m,hidden,ff,shared,experts,identity,top", [(1, 32, 8, 8, 1, 0, 1), (9, 64, 24, 40, 5, 2, 2), (300, 72, 40, 8, 3, 1, 1),
+                                                                     (33, 128, 64, 128, 4, 3, 4), (700, 256, 136, 200, 5, 0, 2), (8, 512, 320, 320, 8, 1, 2)])
+def test_a_shared_expert_runs_as_pieces_that_every_token_uses(ops, dtype, m, hidden, ff, shared, experts, identity, top):
+    """The shared expert cut into pieces of the experts' width (the last filled up with zero rows) in front of the stacked
+    experts: the router's kernel gives every token those pieces with the weight sigmoid(gate logit) and moves the chosen
+    outputs behind them; the whole mixture (chosen experts, identity outputs, shared expert times its gate) equals the
+    plain loop, through the separate launches and through the one launch of a short step."""
+    outputs = experts + identity
     h = rnd(m, hidden, seed=1).to(dtype)
-    u = rnd(m, ff, seed=2, scale=2.0)
-    z = rnd(m, 5, seed=3)                                # the gate's logit is the last column of a wider matrix
-    act = torch.empty(m, ff, dtype=dtype, device=DEV)
-    ops.moe_side(h, u32=u, act=act, gate32=z[:, 4:], kind="relu2")
-    ref = torch.relu(u.double().cpu()) ** 2 * torch.sigmoid(z[:, 4:].double().cpu())
-    assert_close(act, ref, dtype, "activation")
+    w, up, down = expert_weights(experts, hidden, ff, dtype, outputs)
+    w["r.shared.up"] = rnd(shared, hidden, seed=8, scale=hidden ** -0.5).to(dtype)
+    w["r.shared.down"] = rnd(hidden, shared, seed=9, scale=shared ** -0.5).to(dtype)
+    w["r.shared.sg"] = rnd(1, hidden, seed=7, scale=2.0 * hidden ** -0.5).to(dtype)
+    pieces = -(-shared // ff)
+    s_up = torch.zeros(pieces * ff, hidden, dtype=dtype, device=DEV)
+    s_up[:shared] = w["r.shared.up"]
+    s_down = torch.zeros(hidden, pieces * ff, dtype=dtype, device=DEV)
+    s_down[:, :shared] = w["r.shared.down"]
+    up = torch.cat([s_up.view(pieces, ff, hidden), up]).contiguous()
+    down = torch.cat([s_down.view(hidden, pieces, ff).permute(1, 0, 2), down]).contiguous()
+    router = torch.cat([w["r.router"], w["r.shared.sg"]]).contiguous()
+    corr = w["r.correction"].float()
+    mlp = {"router": {"experts": experts, "identity": identity, "top": top}, "shared": {"ff": shared}}
+    wd = {k: v.double().cpu() for k, v in w.items()}
+    chosen, weights = plain.route(mlp, wd, "r", h.double().cpu())
+    ref = plain.mixture(mlp, wd, "r", h.double().cpu())
+    gate = torch.sigmoid(h.double().cpu() @ wd["r.shared.sg"].t())
+    before = rnd(m, hidden, seed=3)
+    for short in (False, True):
+        sel_e = torch.full((m, top + pieces), -1, dtype=torch.int32, device=DEV)
+        sel_w = torch.zeros(m, top + pieces, dtype=torch.float32, device=DEV)
+        options = dict(score="softmax", renormalize=True, correction32=corr, always=pieces)
+        plan = None
+        if short:
+            plan = ops.moe_step(h, router, top, up, down, sel_e, sel_w, n_real=experts + pieces, extra=1, **options)
+            if plan is None:
+                continue        # too large for one block
+        else:
+            z = (h.double() @ router.double().t()).float()
+            ops.moe_route(z[:, :outputs], top, sel_e, sel_w, **options)
+        assert (sel_e[:, :top].cpu() - pieces).tolist() == chosen and sel_e[:, top:].cpu().tolist() == [list(range(pieces))] * m
+        assert_close(sel_w[:, :top], torch.stack(weights), torch.float32, "weights")
+        assert_close(sel_w[:, top:], gate.expand(m, pieces), torch.float32, "the shared expert's gate")
+        out = before.clone()
+        ops.moe_experts(h, sel_e, sel_w, up, down, out, plan=plan, gated=False, weight_on="output", outputs=outputs + pieces)
+        if identity:
+            ops.moe_identity(h, out, sel_e, sel_w, experts + pieces)
+        assert_close(out - before, ref, dtype, "mixture with a shared expert" + (" (short step)" if short else ""))
 
 
 # ------------------------------------------------------------------------------------------ operands of the attention

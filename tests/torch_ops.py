@@ -442,7 +442,15 @@ class TorchOps:
         if clear:
             y32.zero_()
 
-    def moe_route(self, z32, top, sel_e, sel_w, score="sigmoid", renormalize=False, correction32=None):
+    def moe_route(self, z32, top, sel_e, sel_w, score="sigmoid", renormalize=False, correction32=None, always=0):
+        if always:      # the pieces of a shared expert: experts 0..always-1 for every token, weighted by the gate behind the router's logits
+            wide = torch.as_strided(z32, (z32.shape[0], z32.shape[1] + 1), z32.stride())
+            gate = torch.sigmoid(wide[:, -1:].double()).to(torch.float32)
+            e, w = torch.empty_like(sel_e[:, :top]), torch.empty_like(sel_w[:, :top])
+            self.moe_route(z32, top, e, w, score, renormalize, correction32)
+            sel_e.copy_(torch.cat([e + always, torch.arange(always, dtype=torch.int32).expand(z32.shape[0], always)], dim=1))
+            sel_w.copy_(torch.cat([w, gate.expand(z32.shape[0], always)], dim=1))
+            return
         z = z32.double()
         if score == "sigmoid" and not renormalize and correction32 is None:
             order = torch.sort(z, dim=-1, descending=True, stable=True).indices[:, :top]
@@ -476,16 +484,9 @@ class TorchOps:
                 acc[t] += w_res * (w_down[e].double() @ act)
         out32.copy_(acc.to(torch.float32))
 
-    def moe_side(self, h, out32=None, sel_e=None, sel_w=None, n_real=0, u32=None, act=None, gate32=None, kind="relu2"):
-        if sel_e is not None:
-            w = (sel_w.double() * (sel_e >= n_real)).sum(-1, keepdim=True)
-            out32.copy_((out32.double() + w * h.double()).to(torch.float32))
-        if act is not None:
-            u = u32.double()
-            f = torch.relu(u) ** 2 if kind == "relu2" else u
-            if gate32 is not None:
-                f = f * torch.sigmoid(gate32.double().reshape(-1, 1))
-            act.copy_(f.to(act.dtype))
+    def moe_identity(self, h, out32, sel_e, sel_w, n_real):
+        w = (sel_w.double() * (sel_e >= n_real)).sum(-1, keepdim=True)
+        out32.copy_((out32.double() + w * h.double()).to(torch.float32))
 
     def argmax(self, logits, out):
         out.copy_(torch.argmax(logits, dim=-1).to(out.dtype))
