@@ -67,6 +67,13 @@ __device__ __forceinline__ void prepare_unit(const float* __restrict__ qkv, int 
     float norm = 1.0f;
     if (gain != nullptr && (flags & FXP_NORM_WHOLE)) {
         norm = is_q ? whole_q : whole_k;
+        if (norm < 0.f) {       // not summed by the caller: this warp sums the whole projection itself (steps of few tokens)
+            const int n_all = (is_q ? heads : kv_heads) * dk;
+            const float* all = qkv + (size_t)t * ld + (is_q ? 0 : (size_t)heads * dk);
+            float ss = 0.f;
+            for (int c = lane; c < n_all; c += 32) ss = fmaf(all[c], all[c], ss);
+            norm = 1.0f / sqrtf(warp_sum(ss) / (float)n_all + eps);
+        }
         gain += (size_t)head * dk;
     } else if (gain != nullptr) {
         float ss = 0.f;
@@ -107,9 +114,10 @@ __device__ __forceinline__ void prepare_unit(const float* __restrict__ qkv, int 
     __syncwarp();       // x_s is the warp's own and may be filled again for its next unit
 }
 
-// Without FXP_NORM_WHOLE: a warp per (token, head of q, k or v), four of them a block. With it: a block per token, which
-// first sums the squares of the token's whole q and whole k (one fixed order of additions, whatever the batch), then its
-// warps take the token's heads in turn.
+// A warp per (token, head of q, k or v), four of them a block; with FXP_NORM_WHOLE such a warp sums the squares of the
+// token's whole projection itself. With `by_token` (FXP_NORM_WHOLE and many tokens): a block per token, which first sums
+// the squares of the token's whole q and whole k once, then its warps take the token's heads in turn. Either way the
+// additions of a token's sum have one fixed order within a launch; the two orders differ by rounding.
 template <typename T>
 __global__ void __launch_bounds__(FX_WARPS * 32)
 attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ q_out, const float* __restrict__ q_gain,
@@ -117,13 +125,13 @@ attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ 
                          const int* __restrict__ positions, const int* __restrict__ req_index, const int* __restrict__ block_table,
                          int bt_stride, int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages,
                          int tokens, int heads, int kv_heads, int dk, int dv, int writes, int flags,
-                         const float* __restrict__ v_first, int ld_first, const float* __restrict__ vmix) {
+                         const float* __restrict__ v_first, int ld_first, const float* __restrict__ vmix, int by_token) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
     __shared__ float x_s[FX_WARPS][FX_MAX_D];
     __shared__ float red[2][FX_WARPS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (flags & FXP_NORM_WHOLE) {
+    if (by_token) {
         const int t = blockIdx.x;
         const float* row = qkv + (size_t)t * ld;
         const int nq = heads * dk, nk = kv_heads * dk;
@@ -147,7 +155,7 @@ attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ 
     const long long wid = (long long)blockIdx.x * FX_WARPS + warp;
     if (wid >= (long long)tokens * units) return;
     prepare_unit<T>(qkv, ld, q_out, q_gain, k_gain, eps, freq, rot, positions, req_index, block_table, bt_stride, page_size, k_pages, v_pages,
-                    num_pages, heads, kv_heads, dk, dv, writes, flags, v_first, ld_first, vmix, (int)(wid / units), (int)(wid % units), 1.0f, 1.0f,
+                    num_pages, heads, kv_heads, dk, dv, writes, flags, v_first, ld_first, vmix, (int)(wid / units), (int)(wid % units), -1.0f, -1.0f,
                     x_s[warp], lane);
 }
 
@@ -166,15 +174,17 @@ NIB_API int nib_attention_prepare(const float* qkv, int ld, void* q_out, const f
     NIB_REQUIRE(v_first == nullptr || (vmix != nullptr && ld_first >= kv_heads * dv && !(flags & FXP_VALUES_ARE_KEYS)),
                 "attention_prepare: a blend of values needs its factor and rows of at least kv_heads * dv floats");
     if (tokens == 0) return 0;
-    const dim3 grid((flags & FXP_NORM_WHOLE) ? tokens : ceil_div((long long)tokens * (heads + 2 * kv_heads), FX_WARPS)), block(FX_WARPS * 32);
+    // a block per token pays when the tokens alone fill the GPU; a step of few tokens wants a warp per head
+    const int by_token = ((flags & FXP_NORM_WHOLE) && tokens >= 512) ? 1 : 0;
+    const dim3 grid(by_token ? tokens : ceil_div((long long)tokens * (heads + 2 * kv_heads), FX_WARPS)), block(FX_WARPS * 32);
     if (dtype == NIB_F32)
         NIB_CUDA(launch_pdl(attention_prepare_kernel<float>, grid, block, (size_t)0, stream, qkv, ld, (float*)q_out, q_gain, k_gain, eps, freq, rot,
                             positions, req_index, block_table, bt_stride, page_size, (float*)k_pages, (float*)v_pages, num_pages, tokens, heads,
-                            kv_heads, dk, dv, writes, flags, v_first, ld_first, vmix));
+                            kv_heads, dk, dv, writes, flags, v_first, ld_first, vmix, by_token));
     else if (dtype == NIB_BF16)
         NIB_CUDA(launch_pdl(attention_prepare_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, qkv, ld, (__nv_bfloat16*)q_out, q_gain, k_gain,
                             eps, freq, rot, positions, req_index, block_table, bt_stride, page_size, (__nv_bfloat16*)k_pages,
-                            (__nv_bfloat16*)v_pages, num_pages, tokens, heads, kv_heads, dk, dv, writes, flags, v_first, ld_first, vmix));
+                            (__nv_bfloat16*)v_pages, num_pages, tokens, heads, kv_heads, dk, dv, writes, flags, v_first, ld_first, vmix, by_token));
     else
         NIB_REQUIRE(false, "attention_prepare: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();
