@@ -64,6 +64,16 @@ CFG_C = model(300, 128, [
 ], emb=6.0, logit=1.0)
 
 
+# Heads of 64 and 128 with values as wide as keys: in bfloat16 prompt portions take the attention kernel with scores in tensor
+# memory (cap, chunk, window and sink in its softmax warps), decoded tokens the mma.sync kernel with split keys.
+CFG_D = model(200, 128, [
+    windowed(4, 2, 64, 64, 70, 32, 1e6, mlp=dense(96)),
+    chunked(4, 2, 64, 64, 48, mlp=moe(6, 2, 32, identity=1, shared=64)),
+    windowed(2, 1, 128, 128, 129, 64, 1e4, cap=50.0, mlp=moe(4, 1, 64)),
+    chunked(8, 1, 128, 128, 100, mlp=None),
+], emb=5.0, logit=1.0)
+
+
 def make_weights(plan, seed):
     """bfloat16 tensors for every tensor of ``plan``: matrices N(0, 1.2^2 / fan_in), so activations stay of order one."""
     g = torch.Generator().manual_seed(seed)

@@ -13,7 +13,7 @@ import pytest
 import torch
 
 import plain_dusilorn as plain
-from dusilorn_util import (CFG_A, CFG_B, CFG_C, assert_within_rounding, chunked, dense, mixed_schedule, model, moe, pin_routing, plain_logits,
+from dusilorn_util import (CFG_A, CFG_B, CFG_C, CFG_D, assert_within_rounding, chunked, dense, mixed_schedule, model, moe, pin_routing, plain_logits,
                            random_config, tokens, windowed, write_model)
 from gpu_util import assert_close
 from torch_ops import TorchOps
@@ -411,7 +411,7 @@ def folders(tmp_path_factory):
     rounding cannot change (the bfloat16 tests: two choice scores that differ in the third digit would otherwise decide
     whether a position passes)."""
     out = {}
-    for name, cfg, seed in (("A", CFG_A, 11), ("B", CFG_B, 12), ("C", CFG_C, 13)):
+    for name, cfg, seed in (("A", CFG_A, 11), ("B", CFG_B, 12), ("C", CFG_C, 13), ("D", CFG_D, 14)):
         out[name] = write_model(str(tmp_path_factory.mktemp("dus_" + name.lower())), cfg, seed)
         out[name + "/pinned"] = write_model(str(tmp_path_factory.mktemp("dus_pin_" + name.lower())), cfg, seed, weights=pin_routing(cfg))
     return out
@@ -453,7 +453,7 @@ def vocab_of(folder):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,n,page", [("A", 45, 4), ("B", 141, 8), ("C", 300, 16)])
+@pytest.mark.parametrize("name,n,page", [("A", 45, 4), ("B", 141, 8), ("C", 300, 16), ("D", 330, 16)])
 def test_engine_prompts_decoding_and_portions_equal_plain(folders, dtype, name, n, page):
     folder = folder_for(folders, name, dtype)
     ids = tokens(n, vocab_of(folder), 5)
@@ -631,6 +631,38 @@ def test_larger_configurations_under_a_mixed_schedule(seed, dtype, tmp_path):
     eng.check_device()
     for r in range(6):
         judge(d, dtype)(torch.cat(got[r]), plain_logits(d, seqs[r]), seqs[r], f"request {r}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_mixed_schedule_with_heads_of_64_and_128(folders, dtype):
+    """Five requests, four live, portions of 2 to 100 tokens beside single tokens on the model whose prompt portions take the
+    attention kernel with scores in tensor memory; pages of 16 in a pool made for four."""
+    from nanoinfer_b200.engine import StepEntry
+    rng = random.Random(5)
+    folder = folder_for(folders, "D", dtype)
+    lens = [211, 97, 160, 75, 130]
+    seqs = [tokens(n, 200, 70 + i) for i, n in enumerate(lens)]
+    plan = mixed_schedule(rng, lens)
+    eng = gpu_engine(folder, dtype, page=16, pages=4 * (-(-max(lens) // 16) + 1) + 2, slots=4)
+    got, at, live = {i: [] for i in range(5)}, {i: 0 for i in range(5)}, {}
+    for step in plan:
+        entries = []
+        for r, c in step:
+            if r not in live:
+                live[r] = eng.open(f"r{r}")
+            entries.append(StepEntry(live[r], seqs[r][at[r]:at[r] + c], list(range(c))))
+        logits = eng.step(entries).clone()
+        row = 0
+        for r, c in step:
+            got[r].append(logits[row:row + c])
+            row += c
+            at[r] += c
+            if at[r] == lens[r]:
+                eng.close(live.pop(r))
+        eng.cache.check()
+    eng.check_device()
+    for r in range(5):
+        judge(folder, dtype)(torch.cat(got[r]), plain_logits(folder, seqs[r]), seqs[r], f"request {r}")
 
 
 def test_trace_replay_as_a_child_process(folders, tmp_path):
