@@ -159,6 +159,133 @@ attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ 
                     x_s[warp], lane);
 }
 
+
+// ---- the same for bfloat16 storage, eight elements a thread --------------------------------------------------------------
+// A block per token; a work item is eight consecutive elements of a head (two 16-byte loads of floats, one 16-byte store of
+// bfloat16), or, inside the rotated part of a q or k head, the eight elements at c and their mates at c + rot/2 together,
+// so that an angle's sine and cosine are formed once a pair. Takes: no norm or the norm over the whole projection, pairs
+// (i, i + rot/2) with rot a multiple of 16, head sizes in multiples of 8, values of their own (blended or not). The token's
+// page and slot are looked up once. Same arithmetic per element as the kernel above.
+__device__ __forceinline__ void load8(const float* p, float (&x)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&x)[8]) {
+    uint4 u;
+    __nv_bfloat162 t;
+    t = __floats2bfloat162_rn(x[0], x[1]); u.x = *reinterpret_cast<unsigned*>(&t);
+    t = __floats2bfloat162_rn(x[2], x[3]); u.y = *reinterpret_cast<unsigned*>(&t);
+    t = __floats2bfloat162_rn(x[4], x[5]); u.z = *reinterpret_cast<unsigned*>(&t);
+    t = __floats2bfloat162_rn(x[6], x[7]); u.w = *reinterpret_cast<unsigned*>(&t);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+
+__global__ void __launch_bounds__(128)
+attention_prepare_vec_kernel(const float* __restrict__ qkv, int ld, __nv_bfloat16* __restrict__ q_out, const float* __restrict__ q_gain,
+                             const float* __restrict__ k_gain, float eps, const float* __restrict__ freq, int rot,
+                             const int* __restrict__ positions, const int* __restrict__ req_index, const int* __restrict__ block_table,
+                             int bt_stride, int page_size, __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, int num_pages,
+                             int heads, int kv_heads, int dk, int dv, int writes, const float* __restrict__ v_first, int ld_first,
+                             const float* __restrict__ vmix) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
+    __shared__ float red[2][4];
+    const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const float* row = qkv + (size_t)t * ld;
+    const int nq = heads * dk, nk = kv_heads * dk;
+    float whole_q = 1.0f, whole_k = 1.0f;
+    if (q_gain != nullptr) {        // the norm over the whole projection: one sum of squares for q, one for k
+        float sq = 0.f, sk = 0.f;
+        for (int c = tid * 4; c < nq; c += 128 * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(row + c);
+            sq = fmaf(v.x, v.x, sq); sq = fmaf(v.y, v.y, sq); sq = fmaf(v.z, v.z, sq); sq = fmaf(v.w, v.w, sq);
+        }
+        for (int c = tid * 4; c < nk; c += 128 * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(row + nq + c);
+            sk = fmaf(v.x, v.x, sk); sk = fmaf(v.y, v.y, sk); sk = fmaf(v.z, v.z, sk); sk = fmaf(v.w, v.w, sk);
+        }
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        if (lane == 0) { red[0][warp] = sq; red[1][warp] = sk; }
+        __syncthreads();
+        sq = (red[0][0] + red[0][1]) + (red[0][2] + red[0][3]);
+        sk = (red[1][0] + red[1][1]) + (red[1][2] + red[1][3]);
+        whole_q = 1.0f / sqrtf(sq / (float)nq + eps);
+        whole_k = 1.0f / sqrtf(sk / (float)nk + eps);
+    }
+    const int pos = positions[t];
+    long long slot = -1;        // (page * kv_heads) * page_size + offset in the page; a kv head adds head * page_size
+    if (writes) {
+        const int page = block_table[(size_t)req_index[t] * bt_stride + pos / page_size];
+        if (page >= 0 && page < num_pages) slot = (long long)page * kv_heads * page_size + (pos % page_size);   // else: a padding row of a replayed step
+    }
+    const int half = rot >> 1;
+    const int per_head = half / 8 + (dk - rot) / 8;             // work items of a q or k head
+    const int items_qk = (heads + kv_heads) * per_head, items_v = kv_heads * (dv / 8);
+    const float lam = v_first != nullptr ? vmix[0] : 0.f;
+    for (int it = tid; it < items_qk + items_v; it += 128) {
+        if (it >= items_qk) {                                   // eight elements of a value head
+            if (slot < 0) continue;
+            const int c = (it - items_qk) * 8, head = c / dv, off = c - head * dv;
+            float x[8];
+            load8(row + nq + nk + c, x);
+            if (v_first != nullptr) {
+                float f[8];
+                load8(v_first + (size_t)t * ld_first + c, f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] = (1.0f - lam) * x[e] + lam * f[e];
+            }
+            store8(v_pages + ((size_t)slot + (size_t)head * page_size) * dv + off, x);
+            continue;
+        }
+        const int hq = it / per_head, w = it - hq * per_head;  // head among q's then k's; item within it
+        const bool is_q = hq < heads;
+        const int head = is_q ? hq : hq - heads;
+        if (!is_q && slot < 0) continue;
+        const float* src = row + (size_t)hq * dk;                // q heads and k heads lie one behind the other
+        const float* gain = is_q ? q_gain : k_gain;
+        const float norm = is_q ? whole_q : whole_k;
+        __nv_bfloat16* dst = is_q ? q_out + (size_t)t * nq + (size_t)head * dk
+                                  : k_pages + ((size_t)slot + (size_t)head * page_size) * dk;
+        if (w < half / 8) {                                     // eight rotated pairs: elements c.. and c + rot/2..
+            const int c = w * 8;
+            float a[8], b[8];
+            load8(src + c, a);
+            load8(src + c + half, b);
+            if (gain != nullptr) {
+                float ga[8], gb[8];
+                load8(gain + (size_t)head * dk + c, ga);
+                load8(gain + (size_t)head * dk + c + half, gb);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { a[e] = a[e] * norm * ga[e]; b[e] = b[e] * norm * gb[e]; }
+            }
+            float fr[8];
+            load8(freq + c, fr);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float sn, cs;
+                sincosf((float)pos * fr[e], &sn, &cs);
+                const float u = a[e], v = b[e];
+                a[e] = u * cs - v * sn;
+                b[e] = v * cs + u * sn;
+            }
+            store8(dst + c, a);
+            store8(dst + c + half, b);
+        } else {                                                // eight elements that are not rotated
+            const int c = rot + (w - half / 8) * 8;
+            float a[8];
+            load8(src + c, a);
+            if (gain != nullptr) {
+                float ga[8];
+                load8(gain + (size_t)head * dk + c, ga);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) a[e] = a[e] * norm * ga[e];
+            }
+            store8(dst + c, a);
+        }
+    }
+}
+
 NIB_API int nib_attention_prepare(const float* qkv, int ld, void* q_out, const float* q_gain, const float* k_gain, float eps,
                                   const float* freq, int rot, const int* positions, const int* req_index, const int* block_table,
                                   int bt_stride, int page_size, void* k_pages, void* v_pages, int num_pages, int tokens, int heads,
@@ -174,6 +301,18 @@ NIB_API int nib_attention_prepare(const float* qkv, int ld, void* q_out, const f
     NIB_REQUIRE(v_first == nullptr || (vmix != nullptr && ld_first >= kv_heads * dv && !(flags & FXP_VALUES_ARE_KEYS)),
                 "attention_prepare: a blend of values needs its factor and rows of at least kv_heads * dv floats");
     if (tokens == 0) return 0;
+    // bfloat16 storage in the common forms, with enough tokens to fill the GPU with a block each: eight elements a thread
+    const bool aligned16 = ((uintptr_t)qkv % 16 == 0) && ld % 4 == 0 && (uintptr_t)q_out % 16 == 0 && (!writes || ((uintptr_t)k_pages % 16 == 0 && (uintptr_t)v_pages % 16 == 0))
+        && (q_gain == nullptr || ((uintptr_t)q_gain % 16 == 0 && (uintptr_t)k_gain % 16 == 0)) && (rot == 0 || (uintptr_t)freq % 16 == 0)
+        && (v_first == nullptr || ((uintptr_t)v_first % 16 == 0 && ld_first % 4 == 0));
+    if (dtype == NIB_BF16 && tokens >= 256 && aligned16 && dk % 8 == 0 && dv % 8 == 0 && rot % 16 == 0 && (flags & ~FXP_NORM_WHOLE) == 0
+        && ((q_gain != nullptr) == ((flags & FXP_NORM_WHOLE) != 0))) {
+        NIB_CUDA(launch_pdl(attention_prepare_vec_kernel, dim3(tokens), dim3(128), (size_t)0, stream, qkv, ld, (__nv_bfloat16*)q_out, q_gain, k_gain, eps, freq,
+                            rot, positions, req_index, block_table, bt_stride, page_size, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, heads,
+                            kv_heads, dk, dv, writes, v_first, ld_first, vmix));
+        NIB_LAUNCH_CHECK();
+        return 0;
+    }
     // a block per token pays when the tokens alone fill the GPU; a step of few tokens wants a warp per head
     const int by_token = ((flags & FXP_NORM_WHOLE) && tokens >= 512) ? 1 : 0;
     const dim3 grid(by_token ? tokens : ceil_div((long long)tokens * (heads + 2 * kv_heads), FX_WARPS)), block(FX_WARPS * 32);

@@ -241,9 +241,50 @@ def rows_of(pages, bt, req, positions, page):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,kv,dim,vdim,page", [(4, 2, 12, 6, 4), (3, 1, 16, 10, 4), (8, 2, 64, 48, 16), (5, 5, 4, 2, 8), (2, 1, 136, 24, 16)])
-def test_operands_normed_over_the_whole_projection_and_values_blended(ops, dtype, heads, kv, dim, vdim, page):
-    q_lens, before = [5, 1, 9], [3, 17, 0]
+@pytest.mark.parametrize("q_lens,before", [([4, 1], [0, 9]), ([280, 1, 3], [5, 700, 0])])
+@pytest.mark.parametrize("heads,kv,dim,vdim,rot,page", [(4, 2, 12, 6, 8, 4), (8, 2, 96, 48, 48, 16), (16, 2, 64, 64, 32, 16), (2, 1, 128, 128, 128, 8),
+                                                        (3, 3, 40, 8, 16, 4), (2, 2, 32, 16, 0, 16)])
+def test_operands_rotated_in_half_split_pairs_and_values_blended(ops, dtype, heads, kv, dim, vdim, rot, page, q_lens, before):
+    """The first ``rot`` elements of every q and k head turned by position (element i with i + rot/2), the rest unchanged,
+    values blended; both kernels (a warp per head; eight elements a thread), read back from the pages."""
+    ctx, bt, num_pages = batch(q_lens, before, page_size=page)
+    m, nq, nk, nv = sum(q_lens), heads * dim, kv * dim, kv * vdim
+    qkv = rnd(m, nq + nk + nv, seed=1, scale=1.5)
+    first = rnd(m, nv, seed=2)
+    lam = torch.tensor([0.8], device=DEV)
+    freq = torch.tensor([10000.0 ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float64).float().to(DEV) if rot else None
+    kp = torch.zeros(num_pages, kv, page, dim, dtype=dtype, device=DEV)
+    vp = torch.zeros(num_pages, kv, page, vdim, dtype=dtype, device=DEV)
+    q = torch.empty(m, nq, dtype=dtype, device=DEV)
+    ops.attention_prepare(qkv, q, heads, kv, dim, vdim, None, None, 1e-6, freq, rot, ctx, bt, page, kp, vp, True, v_first32=first, vmix32=lam)
+    x = qkv.double().cpu()
+    row = 0
+    for r, (n, b) in enumerate(zip(q_lens, before)):
+        xq, xk = x[row:row + n, :nq].view(n, heads, dim), x[row:row + n, nq:nq + nk].view(n, kv, dim)
+        if rot:     # the design forms the angle in 32-bit: position times frequency, rounded once
+            ang = (torch.arange(b, b + n, dtype=torch.float32)[:, None] * freq.cpu()[None, :]).double()
+            cs, sn = ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+            def turn(y):
+                u, v = y[..., :rot // 2].clone(), y[..., rot // 2:rot].clone()
+                y = y.clone()
+                y[..., :rot // 2], y[..., rot // 2:rot] = u * cs - v * sn, v * cs + u * sn
+                return y
+            xq, xk = turn(xq), turn(xk)
+        assert_close(q[row:row + n], xq.reshape(n, nq), dtype, "queries")
+        assert_close(rows_of(kp, bt.cpu(), r, range(b, b + n), page).reshape(n, nk), xk.reshape(n, nk), dtype, "cached keys")
+        ref_v = 0.2 * x[row:row + n, nq + nk:] + 0.8 * first.double().cpu()[row:row + n]
+        assert_close(rows_of(vp, bt.cpu(), r, range(b, b + n), page).reshape(n, nv), ref_v, dtype, "cached values")
+        row += n
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("q_lens,before", [([5, 1, 9], [3, 17, 0]), ([300, 2, 270], [0, 40, 33])])
+@pytest.mark.parametrize("heads,kv,dim,vdim,page", [(4, 2, 12, 6, 4), (3, 1, 16, 10, 4), (8, 2, 64, 48, 16), (5, 5, 4, 2, 8), (2, 1, 136, 24, 16),
+                                                    (16, 2, 128, 128, 16), (3, 3, 96, 8, 8)])
+def test_operands_normed_over_the_whole_projection_and_values_blended(ops, dtype, heads, kv, dim, vdim, page, q_lens, before):
+    """Steps of few tokens (a warp per head) and of hundreds (a block per token; in bfloat16 with widths in multiples of 8,
+    eight elements a thread)."""
     ctx, bt, num_pages = batch(q_lens, before, page_size=page)
     m, nq, nk, nv = sum(q_lens), heads * dim, kv * dim, kv * vdim
     wide = rnd(m, nq + nk + nv + 3, seed=1, scale=1.5)   # rows that lie apart
