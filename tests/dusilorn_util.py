@@ -19,14 +19,14 @@ def moe(experts, top, ff, identity=0, shared=None):
     return m
 
 
-def chunked(heads, kv_heads, dim, vdim, size, cap=20.0, v_mix=True, scale=None, mlp=None):
+def chunked(heads, kv_heads, dim, vdim, size, cap=25.0, v_mix=True, scale=None, mlp=None):
     """A layer of type ``attention``: whole-projection q/k norm, chunked mask, sink."""
     m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": size}, "softcap": cap, "v_mix": v_mix,
          "scale": scale if scale is not None else 1.5 / dim ** 0.5}
     return {"type": "attention", "mixer": m, "mlp": mlp}
 
 
-def windowed(heads, kv_heads, dim, vdim, size, rot_dims, base, cap=20.0, v_mix=True, scale=None, mlp=None):
+def windowed(heads, kv_heads, dim, vdim, size, rot_dims, base, cap=25.0, v_mix=True, scale=None, mlp=None):
     """A layer of type ``attention_2``: rotated q and k, sliding window."""
     m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": size}, "softcap": cap, "v_mix": v_mix,
          "rot": {"dims": rot_dims, "base": base}, "scale": scale if scale is not None else dim ** -0.5}
@@ -54,7 +54,7 @@ CFG_B = model(77, 96, [
     windowed(6, 3, 32, 16, 33, 16, 30000.0, mlp=dense(64)),
     windowed(2, 2, 16, 24, 8, 16, 1000.0, cap=30.0, mlp=moe(4, 1, 32)),
     chunked(8, 1, 16, 48, 64, mlp=moe(2, 2, 64, identity=3)),
-], emb=4.0, logit=2.0)
+], emb=4.0, logit=2.5)
 # Larger: pages of 16 and prompts of a few hundred tokens cross many pages, chunks and windows; key tiles of 64.
 CFG_C = model(300, 128, [
     windowed(8, 2, 64, 32, 70, 32, 1e6, mlp=dense(192)),
@@ -184,8 +184,8 @@ def random_config(rng, small=True):
         g, vd = (kv, vdim) if v_mix else (rng.choice([1, 2]), rng.choice([4, 8, 16] if small else [16, 32]))
         heads = g * rng.choice([1, 2, 4])
         dim = rng.choice([4, 8, 12, 16, 24, 40, 64, 136] if small else [32, 64, 96, 128])
-        cap = rng.choice([0.0, 5.0, 20.0, 50.0])
-        size = rng.choice([1, 2, 5, 16, 17, 31, 32, 33, 64, 100] if small else [16, 48, 64, 96, 100, 136])
+        cap = rng.choice([0.0, 5.0, 25.0, 50.0])
+        size = rng.choice([1, 2, 5, 16, 17, 31, 32, 33, 64, 100] if small else [16, 48, 64, 96, 100, 130])
         if rng.random() < 0.5:
             layers.append(chunked(heads, g, dim, vd, size, cap=cap, v_mix=v_mix, scale=rng.choice([None, 0.2]), mlp=mlp))
         else:

@@ -54,7 +54,7 @@ def test_config_reads_every_key_and_round_trips(folders):
     assert plan.embedding.params["scale"] == 2.0 and plan.final_norm.params["gain_scale"] == 1.5 and plan.final_norm.params["gain_offset"] == 1.0
     first, second = plan.layers[0].parts["mixer"], plan.layers[1].parts["mixer"]
     assert first.kind == "flex_attention" and first.params["rot"] == (8, 500.0) and first.params["window"] == 5 and first.params["chunk"] == 0
-    assert not first.params["qk_norm"] and not first.params["sink"] and first.params["v_mix"] is None and first.params["softcap"] == 20.0
+    assert not first.params["qk_norm"] and not first.params["sink"] and first.params["v_mix"] is None and first.params["softcap"] == 25.0
     assert first.params["dim"] == 12 and first.params["vdim"] == 6 and "vmix" not in first.tensors
     assert second.params["qk_norm"] == "whole" and second.params["sink"] and second.params["chunk"] == 3 and second.params["window"] == 0
     assert second.params["rot"] is None and second.params["v_mix"] == "first" and second.params["softcap"] == 5.0

@@ -242,7 +242,7 @@ def rows_of(pages, bt, req, positions, page):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("q_lens,before", [([4, 1], [0, 9]), ([280, 1, 3], [5, 700, 0])])
-@pytest.mark.parametrize("heads,kv,dim,vdim,rot,page", [(4, 2, 12, 6, 8, 4), (8, 2, 96, 48, 48, 16), (16, 2, 64, 64, 32, 16), (2, 1, 128, 128, 128, 8),
+@pytest.mark.parametrize("heads,kv,dim,vdim,rot,page", [(4, 2, 12, 6, 8, 4), (6, 3, 80, 40, 48, 16), (16, 2, 64, 64, 32, 16), (2, 1, 128, 128, 128, 8),
                                                         (3, 3, 40, 8, 16, 4), (2, 2, 32, 16, 0, 16)])
 def test_operands_rotated_in_half_split_pairs_and_values_blended(ops, dtype, heads, kv, dim, vdim, rot, page, q_lens, before):
     """The first ``rot`` elements of every q and k head turned by position (element i with i + rot/2), the rest unchanged,
@@ -280,7 +280,7 @@ def test_operands_rotated_in_half_split_pairs_and_values_blended(ops, dtype, hea
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("q_lens,before", [([5, 1, 9], [3, 17, 0]), ([300, 2, 270], [0, 40, 33])])
-@pytest.mark.parametrize("heads,kv,dim,vdim,page", [(4, 2, 12, 6, 4), (3, 1, 16, 10, 4), (8, 2, 64, 48, 16), (5, 5, 4, 2, 8), (2, 1, 136, 24, 16),
+@pytest.mark.parametrize("heads,kv,dim,vdim,page", [(4, 2, 12, 6, 4), (3, 1, 16, 10, 4), (8, 4, 64, 40, 16), (5, 5, 4, 2, 8), (2, 1, 136, 24, 16),
                                                     (16, 2, 128, 128, 16), (3, 3, 96, 8, 8)])
 def test_operands_normed_over_the_whole_projection_and_values_blended(ops, dtype, heads, kv, dim, vdim, page, q_lens, before):
     """Steps of few tokens (a warp per head) and of hundreds (a block per token; in bfloat16 with widths in multiples of 8,
@@ -321,9 +321,9 @@ def filled_pages(dtype, ctx_lens, bt, num_pages, kv, dim, vdim, page, seed):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv,dim,vdim,window,chunk,page,q_lens,before", [
-    (4, 2, 12, 6, 0, 3, 4, [5, 1, 9], [3, 17, 0]), (8, 2, 64, 48, 0, 64, 16, [70, 1, 1], [130, 200, 63]), (8, 2, 96, 48, 136, 0, 16, [1, 1, 40], [300, 135, 120]),
+    (4, 2, 12, 6, 0, 3, 4, [5, 1, 9], [3, 17, 0]), (8, 4, 64, 40, 0, 48, 16, [70, 1, 1], [130, 200, 47]), (6, 2, 80, 40, 130, 0, 16, [1, 1, 40], [300, 129, 120]),
     (3, 1, 16, 24, 0, 17, 8, [33, 2], [0, 40]), (2, 2, 128, 128, 0, 100, 16, [1, 1, 1, 1], [99, 100, 450, 0]), (6, 3, 40, 8, 9, 0, 4, [12, 1], [4, 30]),
-    (8, 2, 64, 64, 0, 64, 16, [70, 1, 130], [130, 200, 63]), (4, 2, 128, 128, 136, 0, 16, [200, 3], [100, 0]), (16, 2, 64, 64, 100, 0, 64, [300], [17]),
+    (8, 2, 64, 64, 0, 64, 16, [70, 1, 130], [130, 200, 63]), (4, 2, 128, 128, 130, 0, 16, [200, 3], [100, 0]), (16, 2, 64, 64, 100, 0, 64, [300], [17]),
     (4, 4, 128, 128, 0, 1000, 32, [129, 65], [0, 700])])
 def test_attention_with_a_sink_beside_chunks_and_windows(ops, dtype, heads, kv, dim, vdim, window, chunk, page, q_lens, before):
     """The kernels (tensor cores for bfloat16, one token per request with keys split over CTAs included) against the plain
@@ -334,26 +334,26 @@ def test_attention_with_a_sink_beside_chunks_and_windows(ops, dtype, heads, kv, 
     q = rnd(m, heads * dim, seed=4).to(dtype)
     sinks = rnd(heads, seed=5, scale=2.0)
     out = torch.empty(m, heads * vdim, dtype=torch.float32, device=DEV)
-    ops.attention_flex(q, out, heads, kv, dim, vdim, dim ** -0.5, 20.0, None, window, chunk, 1.0, ctx, bt, page, kp, vp, sinks32=sinks)
+    ops.attention_flex(q, out, heads, kv, dim, vdim, dim ** -0.5, 25.0, None, window, chunk, 1.0, ctx, bt, page, kp, vp, sinks32=sinks)
     ref = torch.empty(m, heads * vdim, dtype=torch.float64)
-    TorchOps().attention_flex(q.cpu(), ref, heads, kv, dim, vdim, dim ** -0.5, 20.0, None, window, chunk, 1.0, to_cpu(ctx), bt.cpu(), page,
+    TorchOps().attention_flex(q.cpu(), ref, heads, kv, dim, vdim, dim ** -0.5, 25.0, None, window, chunk, 1.0, to_cpu(ctx), bt.cpu(), page,
                               kp.cpu(), vp.cpu(), sinks32=sinks.cpu())
     assert_close(out, ref, dtype, "attention with a sink")
     if dtype == torch.bfloat16:
         # output in the storage type: prompt portions with heads of 64 or 128 take the kernel with scores in tensor memory
         out_b = torch.empty(m, heads * vdim, dtype=dtype, device=DEV)
-        ops.attention_flex(q, out_b, heads, kv, dim, vdim, dim ** -0.5, 20.0, None, window, chunk, 1.0, ctx, bt, page, kp, vp, sinks32=sinks)
+        ops.attention_flex(q, out_b, heads, kv, dim, vdim, dim ** -0.5, 25.0, None, window, chunk, 1.0, ctx, bt, page, kp, vp, sinks32=sinks)
         assert_close(out_b, ref, dtype, "attention with a sink, output in the storage type")
         assert ops.gemm_tc_error() == 0 and ops.attention_tc_error() == 0
     no_sink = torch.empty_like(out)
-    ops.attention_flex(q, no_sink, heads, kv, dim, vdim, dim ** -0.5, 20.0, None, window, chunk, 1.0, ctx, bt, page, kp, vp)
+    ops.attention_flex(q, no_sink, heads, kv, dim, vdim, dim ** -0.5, 25.0, None, window, chunk, 1.0, ctx, bt, page, kp, vp)
     assert (no_sink - out).abs().max().item() > 1e-3
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("decode", [False, True])
 @pytest.mark.parametrize("kind,size,page", [("chunk", 1, 4), ("chunk", 2, 4), ("chunk", 6, 4), ("chunk", 33, 16), ("chunk", 64, 16), ("chunk", 100, 16),
-                                            ("window", 1, 4), ("window", 5, 4), ("window", 64, 16), ("window", 136, 16), ("window", 257, 64)])
+                                            ("window", 1, 4), ("window", 5, 4), ("window", 64, 16), ("window", 130, 16), ("window", 257, 64)])
 def test_keys_just_inside_and_just_outside_an_edge_with_a_sink(ops, kind, size, page, decode, dtype):
     """All keys are alike but one, whose score stands out and whose value carries a mark. A query sees it while it lies in
     the query's chunk (or window) and not one position later; the sink takes its share either way: with the marked key
@@ -387,7 +387,7 @@ def test_keys_just_inside_and_just_outside_an_edge_with_a_sink(ops, kind, size, 
         assert abs(out[-1, 2].item() - want) < 3e-2, (p, sees, out[-1, :4].tolist(), want)
 
 
-@pytest.mark.parametrize("kind,size,page", [("chunk", 64, 16), ("chunk", 100, 16), ("chunk", 128, 64), ("window", 64, 16), ("window", 136, 16), ("window", 257, 64)])
+@pytest.mark.parametrize("kind,size,page", [("chunk", 64, 16), ("chunk", 100, 16), ("chunk", 128, 64), ("window", 64, 16), ("window", 130, 16), ("window", 257, 64)])
 def test_prompt_portions_with_scores_in_tensor_memory_see_the_same_edges(ops, kind, size, page):
     """Heads of 64 in bfloat16, portions of 80 tokens that end just inside and just outside the edge: the marked key's
     weight beside the sink, as above, on the tcgen05 path (and the same from the mma.sync path when it is pinned)."""
